@@ -544,7 +544,7 @@ MHB_EXPORT int mhb_latent_prep(const float* proj, int nsplit, long long split_st
                                int write_kv, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dr % 2 || dr < 0) return fail("latent_prep: a rotated part of %d elements", dr);
-    if (heads * (d + dr) + rank + dr > ld) return fail("latent_prep: a row of %d holds no q and latent of these sizes", ld);
+    if (heads * (d + dr) + (write_kv ? rank + dr : 0) > ld) return fail("latent_prep: a row of %d holds no q and latent of these sizes", ld);
     const size_t smem = sizeof(float) * (size_t)(dr > 0 ? dr : 2);
     const int threads = row_threads(heads * d > rank ? heads * d : rank);
     MHB_DISPATCH_DTYPE(dtype, CT,

@@ -870,3 +870,216 @@ def maps_combine(a, lam: float, eps: float, post: float, out, gate=None, gate_ns
     _check(lib, lib.mhb_maps_combine(_ptr(a), c_float(lam), c_float(eps), c_float(post), g[0], g[1], g[2], g[3],
                                      _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(H), c_int(dv),
                                      _stream()), "maps_combine")
+
+
+# ---- blocks that normalise a sublayer's result; two activations (csrc/gateparts.cu) ---------------------------
+def _parts_args(t, nsplit, split_stride):
+    if t.dtype != torch.float32 or t.stride(-1) != 1:
+        raise KernelError("a product that joins a float32 sum must be float32 with contiguous rows")
+    return _ptr(t), c_int(nsplit), c_longlong(split_stride)
+
+
+def gated_norm_add(x, delta, weight, eps, *, gate=None, bias=None, copy=None, next_weight=None, next_eps=None,
+                   next_out=None):
+    """x <- x + rms(d * sigmoid(g + bias)) * weight, row by row in float32, in place.  ``delta`` and ``gate`` are
+    Products (float32, possibly split-K parts; the gate may be a run of columns of a wider product); without a
+    gate y = d.  ``copy``: the new rows once more in the compute dtype; ``next_out`` with ``next_weight``: the
+    next norm of the new rows, rms(x) * next_weight, in the compute dtype."""
+    lib = build.load("gateparts")
+    R, H = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("gated_norm_add: the stream must be a contiguous float32 matrix")
+    d = delta.tensor
+    if tuple(d.shape[-2:]) != (R, H) or not d[0 if delta.nsplit > 1 else slice(None)].is_contiguous():
+        raise KernelError("gated_norm_add: the product must be contiguous and of the stream's shape")
+    g = (c_void_p(0), c_int(1), c_longlong(0))
+    g_ld = 0
+    if gate is not None:
+        g = _parts_args(gate.tensor, gate.nsplit, gate.split_stride)
+        g_ld = gate.tensor.stride(-2)
+    outs = [t for t in (copy, next_out) if t is not None]
+    for t in outs:
+        if t.dtype != outs[0].dtype or tuple(t.shape) != (R, H) or not t.is_contiguous():
+            raise KernelError("gated_norm_add: copy and next_out are contiguous, of one dtype and of the stream's shape")
+    odt = dtype_code(outs[0].dtype) if outs else F32
+    _check(lib, lib.mhb_gated_norm_add(_ptr(x), *_parts_args(d, delta.nsplit, delta.split_stride), *g, c_int(g_ld),
+                                       _ptr(bias), _ptr(weight), c_float(eps), _ptr(copy),
+                                       _ptr(next_weight if next_out is not None else None),
+                                       c_float(next_eps if next_eps is not None else eps), _ptr(next_out), c_int(odt),
+                                       c_int(R), c_int(H), _stream()), "gated_norm_add")
+
+
+def polynorm_rows(z, coef, eps, out, nsplit=1, split_stride=0):
+    """out = a rms(z) + b rms(z^2) + c rms(z^3) + e over every row of the float32 product z (powers element by
+    element, each power divided by its own root mean square); coef = (a, b, c, e) float32 on the device."""
+    lib = build.load("gateparts")
+    R, Fd = out.shape
+    if coef.dtype != torch.float32 or coef.numel() != 4 or not out.is_contiguous():
+        raise KernelError("polynorm_rows: four float32 coefficients and a contiguous output")
+    _check(lib, lib.mhb_polynorm_rows(*_parts_args(z, nsplit, split_stride), _ptr(coef), c_float(eps), _ptr(out),
+                                      c_int(dtype_code(out.dtype)), c_int(R), c_int(Fd), _stream()), "polynorm_rows")
+
+
+def softcap_rows(z, cap: float):
+    """z <- cap * tanh(z / cap) in place (float32)."""
+    lib = build.load("gateparts")
+    if z.dtype != torch.float32 or not z.is_contiguous():
+        raise KernelError("softcap_rows: a contiguous float32 tensor")
+    _check(lib, lib.mhb_softcap_rows(_ptr(z), c_float(cap), c_longlong(z.numel()), _stream()), "softcap_rows")
+
+
+# ---- linear attention with a decay per key channel and token (csrc/gatedlinear.cu) ------------------------------
+GATED_LINEAR_MODES = {"gla": 0, "hgrn2": 1}
+
+
+def gated_linear_prep(mode: str, proj, q0, k0, v0, a0, bias, q, k, v, g, *, a2=None, low=None, qscale=1.0, tau=1.0):
+    """From the float32 Product ``proj`` (columns q0 / k0 / v0 / a0, heads side by side) the recurrence's float32
+    inputs q, k, v and g = log(decay).  "gla": q = zq * qscale, k = zk, g = logsigmoid(z + bias) / tau with
+    z = a2 @ (the columns a0 .. a0 + rank of ``proj``), ``a2`` [heads * dim, rank], taken in float32.  "hgrn2":
+    q = silu(zq), f = low + (1 - low) sigmoid(za + bias) with za the columns from a0, k = 1 - f, g = log f."""
+    lib = build.load("gatedlinear")
+    T, QW = q.shape
+    VW = v.shape[1]
+    for t in (q, k, v, g):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError("gated_linear_prep: q, k, v and g are contiguous float32")
+    rank = 0
+    if mode == "gla":
+        if a2 is None or a2.shape[0] != QW or not a2.is_contiguous():
+            raise KernelError("gated_linear_prep: the decay's second matrix is contiguous [heads * dim, rank]")
+        rank = a2.shape[1]
+    _check(lib, lib.mhb_gated_linear_prep(
+        *_parts_args(proj.tensor, proj.nsplit, proj.split_stride), c_int(proj.tensor.stride(-2)), c_int(q0), c_int(k0),
+        c_int(v0), c_int(a0), _ptr(a2), c_int(dtype_code(a2.dtype) if a2 is not None else F32), c_int(rank), _ptr(bias),
+        _ptr(low), c_float(qscale), c_float(1.0 / tau), c_int(GATED_LINEAR_MODES[mode]),
+        _ptr(q), _ptr(k), _ptr(v), _ptr(g), c_int(T), c_int(QW), c_int(VW), _stream()), "gated_linear_prep")
+
+
+def gated_linear_head_norm(o, weight, eps, out, *, heads, dv, gate=None, gate0=0):
+    """out[t, h] = rms(o[t, h]) * weight, one norm per head over its ``dv`` values (``weight`` [dv] is shared by the
+    heads), times silu of the columns gate0 .. of the float32 Product ``gate`` if there is one."""
+    lib = build.load("gatedlinear")
+    T = o.shape[0]
+    if o.dtype != torch.float32 or not o.is_contiguous() or not out.is_contiguous() or o.shape[1] != heads * dv:
+        raise KernelError("gated_linear_head_norm: o is contiguous float32 [T, heads * dv], out contiguous")
+    gp = (c_void_p(0), c_int(1), c_longlong(0))
+    g_ld = 0
+    if gate is not None:
+        gp = _parts_args(gate.tensor, gate.nsplit, gate.split_stride)
+        g_ld = gate.tensor.stride(-2)
+    _check(lib, lib.mhb_gated_linear_head_norm(_ptr(o), _ptr(weight), c_float(eps), *gp, c_int(g_ld), c_int(gate0),
+                                               _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(heads), c_int(dv),
+                                               _stream()), "gated_linear_head_norm")
+
+
+def _gated_linear_head(q, k, g, v, state, out, tok_seg, seg_slot, positions, H, dk, dv):
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (H, dk, dv):
+        raise KernelError(f"gated linear attention: the state must be contiguous float32 [slots, {H}, {dk}, {dv}]")
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("gated linear attention: the output is contiguous float32")
+    return (_ptr(q), _ptr(k), _ptr(g), _ptr(v), _ptr(state), _ptr(out), _ptr(tok_seg), _ptr(seg_slot), _ptr(positions))
+
+
+def gated_linear_scan(q, k, g, v, state, out, tok_seg, seg_slot, positions, *, heads, dk, dv, writable=True,
+                      max_tokens=0):
+    """S <- diag(exp(g_t)) S + k_t v_t^T, o_t = S^T q_t, token by token, for every segment of at most ``max_tokens``
+    tokens (0: all); ``state`` [slots, heads, dk, dv], ``out`` float32 [T, heads * dv]."""
+    lib = build.load("gatedlinear")
+    T, S = out.shape[0], seg_slot.shape[0]
+    head = _gated_linear_head(q, k, g, v, state, out, tok_seg, seg_slot, positions, heads, dk, dv)
+    _check(lib, lib.mhb_gated_linear_scan(*head, c_int(T), c_int(S), c_int(heads), c_int(dk), c_int(dv),
+                                          c_int(1 if writable else 0), c_int(max_tokens), _stream()), "gated_linear_scan")
+
+
+def gated_linear_chunk_smem(dk: int, dv: int, chunk: int) -> int:
+    lib = build.load("gatedlinear")
+    lib.mhb_gated_linear_chunk_smem.restype = c_longlong
+    return int(lib.mhb_gated_linear_chunk_smem(c_int(dk), c_int(dv), c_int(chunk)))
+
+
+def gated_linear_chunked(q, k, g, v, state, out, tok_seg, seg_slot, positions, chunks, num_chunks, seg_chunks,
+                         num_segs, scratch, chunk, *, heads, dk, dv, writable=True):
+    """The same for the listed segments, cut into the listed chunks of at most ``chunk`` tokens; ``scratch`` float32
+    holds num_chunks * heads * (dk * dv + dk)."""
+    lib = build.load("gatedlinear")
+    T = out.shape[0]
+    if scratch.dtype != torch.float32 or scratch.numel() < num_chunks * heads * (dk * dv + dk):
+        raise KernelError("gated_linear_chunked: the scratch is too small")
+    head = _gated_linear_head(q, k, g, v, state, out, tok_seg, seg_slot, positions, heads, dk, dv)
+    _check(lib, lib.mhb_gated_linear_chunked(*head, c_int(T), c_int(heads), c_int(dk), c_int(dv),
+                                             c_int(1 if writable else 0), _ptr(chunks), c_int(num_chunks),
+                                             _ptr(seg_chunks), c_int(num_segs), _ptr(scratch), c_int(chunk), _stream()),
+           "gated_linear_chunked")
+
+
+# ---- routed feed-forward (csrc/moe.cu) --------------------------------------------------------------------------
+MOE_TILE_ROWS = 64
+
+
+def moe_max_tiles(pairs: int, experts: int) -> int:
+    """Upper bound of the tiles that ``pairs`` (token, expert) pairs over ``experts`` experts are cut into."""
+    return -(-pairs // MOE_TILE_ROWS) + min(experts, pairs)
+
+
+def moe_plan_words(pairs: int, experts: int) -> int:
+    return 1 + 3 * moe_max_tiles(pairs, experts) + 2 * pairs
+
+
+def moe_route(logits, correction, chosen, weights, *, outputs, top, groups=1, keep=1):
+    """Per token: softmax over the first ``outputs`` columns of the float32 Product ``logits``, choice by softmax +
+    correction inside the best ``keep`` of ``groups`` groups, ``chosen`` int32 [T, top] and the chosen outputs'
+    softmax values divided by their sum as ``weights`` float32 [T, top]."""
+    lib = build.load("moe")
+    T = chosen.shape[0]
+    _check(lib, lib.mhb_moe_route(*_parts_args(logits.tensor, logits.nsplit, logits.split_stride),
+                                  c_int(logits.tensor.stride(-2)), _ptr(correction), _ptr(chosen), _ptr(weights),
+                                  c_int(T), c_int(outputs), c_int(top), c_int(groups), c_int(keep), _stream()), "moe_route")
+
+
+def moe_plan(chosen, plan, *, experts):
+    """Group the chosen pairs by expert (outputs at or beyond ``experts`` get no row); ``plan`` int32 of
+    moe_plan_words(pairs, experts)."""
+    lib = build.load("moe")
+    T, top = chosen.shape
+    pairs = T * top
+    if plan.dtype != torch.int32 or plan.numel() < moe_plan_words(pairs, experts):
+        raise KernelError("moe_plan: the plan buffer is too small")
+    _check(lib, lib.mhb_moe_plan(_ptr(chosen), c_int(pairs), c_int(top), c_int(experts),
+                                 c_int(moe_max_tiles(pairs, experts)), _ptr(plan), _stream()), "moe_plan")
+
+
+def moe_linear(x, plan, w, out, *, pairs, experts, gather: bool, glu: bool):
+    """out[r] = w[expert of row r] applied to x[token of row r] (``gather``) or to x[r]; ``w`` [experts, N, K], or
+    [experts, 2 N, K] holding gate above up with ``glu`` (then out = silu(gate x) * (up x)); float32 accumulation."""
+    lib = build.load("moe")
+    N, Kd = out.shape[1], x.shape[1]
+    if w.dtype != x.dtype or tuple(w.shape) != (experts, (2 if glu else 1) * N, Kd) or not w.is_contiguous():
+        raise KernelError(f"moe_linear: weights {list(w.shape)} for rows {Kd} wide and outputs {N} wide")
+    if x.stride(1) != 1 or not out.is_contiguous():
+        raise KernelError("moe_linear: contiguous rows")
+    _check(lib, lib.mhb_moe_linear(_ptr(x), c_int(dtype_code(x.dtype)), c_longlong(x.stride(0)), _ptr(plan),
+                                   c_int(moe_max_tiles(pairs, experts)), c_int(pairs), c_int(1 if gather else 0), _ptr(w),
+                                   _ptr(out), c_int(dtype_code(out.dtype)), c_int(N), c_int(Kd), c_int(1 if glu else 0),
+                                   _stream()), "moe_linear")
+
+
+def moe_combine(y, plan, chosen, weights, h, out, *, experts, shared=None, shared_gate=None):
+    """out[t] = sum_k weights[t, k] * (y[row of pair (t, k)], or h[t] for an identity expert) + sigmoid(shared_gate[t])
+    * shared[t]; ``shared`` and ``shared_gate`` are float32 Products (the gate one column)."""
+    lib = build.load("moe")
+    T, top = chosen.shape
+    pairs = T * top
+    W = out.shape[1]
+    if out.dtype != torch.float32 or not out.is_contiguous() or h.stride(1) != 1:
+        raise KernelError("moe_combine: a contiguous float32 output and input rows that are contiguous")
+    sh = (c_void_p(0), c_int(1), c_longlong(0))
+    sg = (c_void_p(0), c_int(1), c_longlong(0))
+    g_ld = 0
+    if shared is not None:
+        sh = _parts_args(shared.tensor, shared.nsplit, shared.split_stride)
+        sg = _parts_args(shared_gate.tensor, shared_gate.nsplit, shared_gate.split_stride)
+        g_ld = shared_gate.tensor.stride(-2)
+    _check(lib, lib.mhb_moe_combine(_ptr(y), _ptr(plan), c_int(moe_max_tiles(pairs, experts)), c_int(pairs), _ptr(chosen),
+                                    _ptr(weights), c_int(top), c_int(experts), _ptr(h), c_int(dtype_code(h.dtype)),
+                                    c_longlong(h.stride(0)), *sh, *sg, c_int(g_ld), _ptr(out), c_int(T), c_int(W),
+                                    _stream()), "moe_combine")

@@ -31,7 +31,8 @@ NVCC_FLAGS = [
 
 # Every module the package has; __graft_entry__.build() compiles all of them.
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_decode",
-           "attention_tc", "sampling", "postnorm", "lightning", "attention_mma_ext", "mixparts")
+           "attention_tc", "sampling", "postnorm", "lightning", "attention_mma_ext", "mixparts", "gateparts", "gatedlinear",
+           "moe")
 
 
 class KernelBuildError(RuntimeError):

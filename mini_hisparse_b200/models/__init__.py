@@ -1,2 +1,2 @@
-from . import dotivik, koronex, qwen2  # noqa: F401  (register Dotivik, Koronex and Qwen2ForCausalLM)
+from . import dotivik, koronex, qwen2, tudasun  # noqa: F401  (register Dotivik, Koronex, Qwen2ForCausalLM and Tudasun)
 from .decoder import DecoderModel

@@ -60,8 +60,9 @@ class DecoderModel:
     def kernel_modules(self) -> tuple[str, ...]:
         """What this model's steps launch: the runtime's libraries and those of its parts."""
         mods = list(self.rt.kernel_modules())
-        for _, part in self.named_parts():
-            for m in part.kernel_modules():
+        users = [part for _, part in self.named_parts()] + list(self.blocks)
+        for user in users:
+            for m in user.kernel_modules():
                 if m not in mods:
                     mods.append(m)
         return tuple(mods)

@@ -334,6 +334,10 @@ class Block:
     def parts(self) -> dict[str, Part]:
         raise NotImplementedError
 
+    def kernel_modules(self) -> tuple[str, ...]:
+        """Kernel libraries the arrangement itself launches, beyond those of its parts."""
+        return ()
+
     def bind(self, shared: dict[str, Part]) -> None:
         """Receive the model's shared parts (ModelSpec.shared) by key; most arrangements need none."""
 

@@ -5,7 +5,7 @@ import torch
 
 from ..kernels import api as K
 from .base import Block, CacheView, Product, StepContext
-from .registry import FEED_FORWARDS, MIXERS, NORMS, register_block
+from .registry import FEED_FORWARDS, GATES, MIXERS, NORMS, register_block
 from .spec import LayerSpec
 
 
@@ -148,3 +148,84 @@ class ParallelBlock(Block):
         a = self.mixer.forward(h, ctx, cache)
         main.wait_event(join)
         return Product(a.tensor, a.nsplit, also=f)
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before AND behind each sublayer, the behind one on the sublayer's result alone:
+
+        h = norm1(x);  x <- x + norm1b(mixer(h) * sigmoid(gate1(h)))
+        h = norm2(x);  x <- x + norm2b(ff(h) * sigmoid(gate2(h)))      (if the layer has a feed-forward)
+        x <- x + side(x)                                              (if the layer has a "side" part)
+
+    Roles: "mixer_norm", "mixer", "mixer_post_norm"; optionally "mixer_gate"; optionally "ff_norm",
+    "feed_forward", "ff_post_norm" and "ff_gate"; optionally "side".  A gate is a part of the gates' registry that
+    gives logits (and a bias) as wide as the stream; without one the sublayer's result is normalised as it is.
+    One kernel multiplies by the gate, normalises, adds into the stream and already applies the norm that the
+    next sublayer opens with; the side branch reads the stream's rows in the compute dtype from the same kernel.
+    """
+
+    keeps_copy = False
+
+    def __init__(self, spec: LayerSpec, rt):
+        self.spec = spec
+        self.mixer_norm = NORMS.build(spec.part("mixer_norm"), rt=rt)
+        self.mixer = MIXERS.build(spec.part("mixer"), rt=rt)
+        self.mixer_post_norm = NORMS.build(spec.part("mixer_post_norm"), rt=rt)
+        self.mixer_gate = GATES.build(spec.part("mixer_gate"), rt=rt) if spec.has("mixer_gate") else None
+        self.feed_forward = self.ff_norm = self.ff_post_norm = self.ff_gate = self.side = None
+        if spec.has("feed_forward"):
+            self.ff_norm = NORMS.build(spec.part("ff_norm"), rt=rt)
+            self.feed_forward = FEED_FORWARDS.build(spec.part("feed_forward"), rt=rt)
+            self.ff_post_norm = NORMS.build(spec.part("ff_post_norm"), rt=rt)
+            self.ff_gate = GATES.build(spec.part("ff_gate"), rt=rt) if spec.has("ff_gate") else None
+        if spec.has("side"):
+            self.side = FEED_FORWARDS.build(spec.part("side"), rt=rt)
+
+    def parts(self):
+        out = {"mixer_norm": self.mixer_norm, "mixer": self.mixer, "mixer_post_norm": self.mixer_post_norm}
+        if self.mixer_gate is not None:
+            out["mixer_gate"] = self.mixer_gate
+        if self.feed_forward is not None:
+            out.update(ff_norm=self.ff_norm, feed_forward=self.feed_forward, ff_post_norm=self.ff_post_norm)
+            if self.ff_gate is not None:
+                out["ff_gate"] = self.ff_gate
+        if self.side is not None:
+            out["side"] = self.side
+        return out
+
+    def kernel_modules(self):
+        return ("gateparts",)
+
+    def bind(self, shared):
+        for part in self.parts().values():
+            if hasattr(part, "bind"):
+                part.bind(shared)
+
+    def _join(self, x, result: Product, gate, h, post, ctx, *, copy=None, then=None, name="gate"):
+        """x <- x + post(result * sigmoid(gate(h))); ``then``: the norm whose output of the new x is wanted too."""
+        if result.also is not None:
+            raise ValueError("a sandwich block normalises one product per sublayer")
+        z = gate.logits(h, ctx, name) if gate is not None else None
+        nxt = ctx.ws.get("h2", tuple(x.shape), ctx.rt.dtype) if then is not None else None
+        K.gated_norm_add(x, result, post.weight, post.eps, gate=z, bias=gate.bias if gate is not None else None,
+                         copy=copy, next_weight=then.weight if then is not None else None,
+                         next_eps=then.eps if then is not None else None, next_out=nxt)
+        return nxt
+
+    def forward(self, x, pending: Product | None, ctx: StepContext, cache: CacheView | None):
+        rt, ws = ctx.rt, ctx.ws
+        h = self.mixer_norm.forward(x, ctx, delta=pending)
+        a = self.mixer.forward(h, ctx, cache)
+        want_copy = self.side is not None and rt.dtype != torch.float32
+        last = self.feed_forward is None
+        copy = ws.get("x_copy", tuple(x.shape), rt.dtype) if want_copy and last else None
+        h2 = self._join(x, a, self.mixer_gate, h, self.mixer_post_norm, ctx, copy=copy,
+                        then=None if last else self.ff_norm, name="gate1")
+        if not last:
+            f = self.feed_forward.forward(h2, ctx)
+            copy = ws.get("x_copy", tuple(x.shape), rt.dtype) if want_copy else None
+            self._join(x, f, self.ff_gate, h2, self.ff_post_norm, ctx, copy=copy, name="gate2")
+        if self.side is not None:
+            self.side.forward_into(x, x if copy is None else copy, ctx, keep_copy=False)
+        return None

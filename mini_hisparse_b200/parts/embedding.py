@@ -114,13 +114,15 @@ class TokenTable(Part):
 @HEADS.register("lm_head")
 class LMHead(Part):
     """logits = h W^T in float32, no bias (mini_hisparse/model.py:96,181).  With ``tied`` the
-    embedding table is the weight and the checkpoint holds no lm_head tensor."""
+    embedding table is the weight and the checkpoint holds no lm_head tensor.  With ``softcap`` c the logits
+    are capped smoothly: logits <- c tanh(logits / c), in float32."""
 
     def __init__(self, spec: PartSpec, rt=None):
         super().__init__(spec, rt)
         self.vocab = int(spec["vocab_size"])
         self.width = int(spec["hidden_size"])
         self.tied = bool(spec["tied"])
+        self.softcap = float(spec.get("softcap") or 0.0)
         self.weight_name = spec.get("weight_name", "weight")
         self.weight = None
 
@@ -136,6 +138,11 @@ class LMHead(Part):
     def tie(self, embedding: TokenEmbedding):
         self.weight = embedding.weight
 
+    def kernel_modules(self):
+        return ("gateparts",) if self.softcap else ()
+
     def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
-        return ctx.rt.linear(h, self.weight, ctx.ws, "logits", out_dtype=torch.float32,
-                             allow_split=False).matrix
+        logits = ctx.rt.linear(h, self.weight, ctx.ws, "logits", out_dtype=torch.float32, allow_split=False).matrix
+        if self.softcap:
+            K.softcap_rows(logits, self.softcap)
+        return logits

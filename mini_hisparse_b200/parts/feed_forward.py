@@ -46,7 +46,10 @@ class SwiGLU(FeedForward):
 @register_feed_forward("mlp_act")
 class ActivatedMLP(FeedForward):
     """down(act(up(x))), no gate, no biases; ``activation``: "relu2" (the square of relu), "silu" or
-    "gelu_tanh", computed in float32 on the product's float32 output.  Tensor names: ``up_name`` and
+    "gelu_tanh", computed in float32 on the product's float32 output, or "polynorm":
+    act(z) = a rms(z) + b rms(z^2) + c rms(z^3) + e with the powers taken element by element, each divided by its
+    own root mean square over the token's ``intermediate_size`` values (``eps`` inside the root), and the four numbers
+    (a, b, c, e) stored as the tensor ``coef_name`` (default "act").  Tensor names: ``up_name`` and
     ``down_name`` (default "up" and "down")."""
 
     def __init__(self, spec: PartSpec, rt=None):
@@ -54,24 +57,38 @@ class ActivatedMLP(FeedForward):
         self.hidden = int(spec["hidden_size"])
         self.inter = int(spec["intermediate_size"])
         self.activation = spec.get("activation", "relu2")
-        if self.activation not in K.ACTIVATIONS or self.activation == "copy":
+        self.polynorm = self.activation == "polynorm"
+        if not self.polynorm and (self.activation not in K.ACTIVATIONS or self.activation == "copy"):
             raise ValueError(f"unknown activation {self.activation!r}")
         self.up_name, self.down_name = spec.get("up_name", "up"), spec.get("down_name", "down")
-        self.up = self.down = None
+        self.coef_name = spec.get("coef_name", "act")
+        self.eps = float(spec["eps"]) if self.polynorm else 0.0
+        self.up = self.down = self.coef = None
+
+    def kernel_modules(self):
+        return ("gateparts",) if self.polynorm else ("postnorm",)
 
     def parameters(self):
-        return {self.up_name: ParamSpec((self.inter, self.hidden)),
-                self.down_name: ParamSpec((self.hidden, self.inter))}
+        p = {self.up_name: ParamSpec((self.inter, self.hidden)),
+             self.down_name: ParamSpec((self.hidden, self.inter))}
+        if self.polynorm:
+            p[self.coef_name] = ParamSpec((4,), role="vector", init=("normal", 0.3, 0.3))
+        return p
 
     def load(self, tensors):
         self.up = tensors[self.up_name].contiguous()
         self.down = tensors[self.down_name].contiguous()
+        if self.polynorm:
+            self.coef = tensors[self.coef_name].contiguous()
 
     def forward(self, h, ctx: StepContext) -> Product:
         rt, ws = ctx.rt, ctx.ws
         z = rt.linear(h, self.up, ws, "ff_up", out_dtype=torch.float32)
         act = ws.get("ff_act", (h.shape[0], self.inter), rt.dtype)
-        K.act_rows(z.tensor, act, self.activation, nsplit=z.nsplit, split_stride=z.split_stride)
+        if self.polynorm:
+            K.polynorm_rows(z.tensor, self.coef, self.eps, act, nsplit=z.nsplit, split_stride=z.split_stride)
+        else:
+            K.act_rows(z.tensor, act, self.activation, nsplit=z.nsplit, split_stride=z.split_stride)
         return rt.linear(act, self.down, ws, "ff_out", out_dtype=torch.float32)       # it joins a float32 sum
 
 
@@ -96,6 +113,9 @@ class TokenSide(FeedForward):
         self.table = None
         self.gate = self.proj = self.norm = None
 
+    def kernel_modules(self):
+        return ("postnorm",)
+
     def parameters(self):
         return {"gate": ParamSpec((self.dim, self.hidden)), "proj": ParamSpec((self.hidden, self.dim)),
                 "norm": ParamSpec((self.hidden,), role="vector", init=("normal", 1.0, 0.1))}
@@ -108,18 +128,20 @@ class TokenSide(FeedForward):
         if self.column0 + self.dim > self.table.width:
             raise ValueError(f"columns {self.column0}..{self.column0 + self.dim} are outside a table {self.table.width} wide")
 
-    def forward_into(self, x, h, ctx: StepContext):
+    def forward_into(self, x, h, ctx: StepContext, keep_copy: bool = True):
         """Add the branch into the float32 stream ``x`` (``h``: its rows in the compute dtype); returns
-        the new rows in the compute dtype."""
+        the new rows in the compute dtype (``keep_copy`` False: nobody reads them, None is returned)."""
         rt, ws = ctx.rt, ctx.ws
         z = rt.linear(h, self.gate, ws, "side_gate", out_dtype=torch.float32)
         g = ws.get("side_g", (h.shape[0], self.dim), rt.dtype)
         K.table_gate(z.tensor, self.table.weight, self.column0, ctx.tokens, g, nsplit=z.nsplit,
                      split_stride=z.split_stride, status=ctx.status)
         y = rt.linear(g, self.proj, ws, "side_out", out_dtype=torch.float32)
-        copy = None if rt.dtype == torch.float32 else ws.get("x_copy", tuple(x.shape), rt.dtype)
+        copy = None if rt.dtype == torch.float32 or not keep_copy else ws.get("x_copy", tuple(x.shape), rt.dtype)
         K.norm_mix(x, self.norm, self.eps, delta=y.tensor, nsplit=y.nsplit, split_stride=y.split_stride,
                    alpha=0.0, keep=1.0, copy=copy)
+        if not keep_copy:
+            return None
         return x if copy is None else copy
 
     def forward(self, h, ctx):

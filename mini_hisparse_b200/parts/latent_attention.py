@@ -19,14 +19,18 @@ class LatentAttention(Mixer):
     * c <- c / sqrt(mean(c^2) + eps) * w_c; kr (rot_dim wide, not normalised) is rotated by the position part
       and is the rotated key part of EVERY head; the rotated part of each q head is rotated the same way.
     * Head i: k_i = [W_uk,i c | kr], v_i = W_uv,i c; s = (q_i . k_i) * scale; causal softmax over the last
-      ``window`` keys (None: all of them); the head's output times sigmoid(W_g h)_i; then W_o.
+      ``window`` keys (None: all of them); the head's output times sigmoid(W_g h)_i (``gate``, default True);
+      then W_o.  With ``sink`` the softmax's denominator has one more term, exp(sink_i): a stored logit per head
+      that stands for no position, brings no value and is not scaled.
+    * ``own_kv`` False: the layer has no W_dkv and no norm weight; it reads the cache rows of another run entry
+      (RunEntry.cache_of), rotated as that entry wrote them, with its own queries, expansions, sink and gate.
     * Only [c | kr] is cached (PagedRowsNeed(kv_rank + rot_dim)).  The expansions are never formed per key:
       q_i . (W_uk,i c) = (W_uk,i^T q_i) . c, so the query is carried into the latent space (one small matrix
       per head), attention runs with the cached row as key AND, in its first kv_rank elements, as value, and
       the output sum_j p_j c_j is expanded once per query by W_uv,i.
 
     Parameters: hidden_size, heads, dim, rot_dim, vdim, kv_rank, scale, window, eps, position (a PartSpec
-    over rot_dim elements).  Tensors: q, dkv, dkv.norm, uk, uv, g, o.  Scores, softmax, the latent's norm,
+    over rot_dim elements), gate, sink, own_kv.  Tensors: q, dkv, dkv.norm, uk, uv, g, sink, o.  Scores, softmax, the latent's norm,
     angles and the gate are float32.
     """
 
@@ -39,6 +43,9 @@ class LatentAttention(Mixer):
         self.scale = float(spec["scale"])
         self.window = spec.get("window")
         self.eps = float(spec["eps"])
+        self.has_gate = bool(spec.get("gate", True))
+        self.has_sink = bool(spec.get("sink", False))
+        self.own_kv = bool(spec.get("own_kv", True))
         self.position = POSITIONS.build(spec["position"], rt=rt)
         if int(getattr(self.position, "rotary_dim", 0) or 0) != self.dr:
             raise ValueError(f"the position part must rotate all {self.dr} elements of the rotated key part")
@@ -46,7 +53,7 @@ class LatentAttention(Mixer):
         if self.rank > 512:
             raise ValueError(f"a latent {self.rank} wide: the attention kernels take values up to 512 wide")
         self.qw, self.ow = self.heads * (self.d + self.dr), self.heads * self.dv
-        self.weight = self.o_weight = self.c_norm = self.uk_t = self.uv = None
+        self.weight = self.o_weight = self.c_norm = self.uk_t = self.uv = self.sink = None
 
     def kernel_family(self, page_size: int | None = None) -> str:
         """"tc": tcgen05 128-row tiles for long portions (bfloat16, a cache row 64 or 128 wide, pages that divide
@@ -84,15 +91,24 @@ class LatentAttention(Mixer):
         return AttentionPlanner(AttentionShape(self.heads, 1, self.window, rows), sm_count)
 
     def parameters(self):
-        return {"q": ParamSpec((self.qw, self.hidden)), "dkv": ParamSpec((self.width, self.hidden)),
-                "dkv.norm": ParamSpec((self.rank,), role="vector", init=("normal", 1.0, 0.1)),
-                "uk": ParamSpec((self.heads * self.d, self.rank)), "uv": ParamSpec((self.heads * self.dv, self.rank)),
-                "g": ParamSpec((self.heads, self.hidden)), "o": ParamSpec((self.hidden, self.ow))}
+        p = {"q": ParamSpec((self.qw, self.hidden)),
+             "uk": ParamSpec((self.heads * self.d, self.rank)), "uv": ParamSpec((self.heads * self.dv, self.rank)),
+             "o": ParamSpec((self.hidden, self.ow))}
+        if self.own_kv:
+            p.update({"dkv": ParamSpec((self.width, self.hidden)),
+                      "dkv.norm": ParamSpec((self.rank,), role="vector", init=("normal", 1.0, 0.1))})
+        if self.has_gate:
+            p["g"] = ParamSpec((self.heads, self.hidden))
+        if self.has_sink:
+            p["sink"] = ParamSpec((self.heads,), role="vector", init=("normal", 0.0, 1.0))
+        return p
 
     def load(self, tensors):
-        self.weight = _pad_rows(torch.cat((tensors["q"], tensors["dkv"], tensors["g"]), 0))       # [q | c | kr | g]
+        rows = [tensors["q"]] + ([tensors["dkv"]] if self.own_kv else []) + ([tensors["g"]] if self.has_gate else [])
+        self.weight = _pad_rows(torch.cat(rows, 0))                                               # [q | c | kr | g]
         self.o_weight = tensors["o"].contiguous()
-        self.c_norm = tensors["dkv.norm"]
+        self.c_norm = tensors.get("dkv.norm")
+        self.sink = tensors.get("sink")
         # per head: the key expansion transposed [rank, dim] (it carries q into the latent space) and the
         # value expansion as stored [vdim, rank]
         self.uk_t = tensors["uk"].view(self.heads, self.d, self.rank).transpose(1, 2).contiguous()
@@ -101,6 +117,8 @@ class LatentAttention(Mixer):
     def forward(self, h, ctx: StepContext, cache: CacheView) -> Product:
         rt, ws, T = ctx.rt, ctx.ws, h.shape[0]
         meta = cache.meta
+        if cache.writable != self.own_kv:
+            raise ValueError("a latent_attention layer with a W_dkv of its own owns its cache, one without reads another's")
         proj = rt.linear(h, self.weight, ws, "la_proj", out_dtype=torch.float32)
         p = proj.tensor
         q_plain = ws.get("la_q_plain", (T, self.heads, self.d), rt.dtype)
@@ -111,9 +129,14 @@ class LatentAttention(Mixer):
                       page_size=cache.page_size, write_kv=cache.writable, nsplit=proj.nsplit,
                       split_stride=proj.split_stride, status=ctx.status)
         K.head_linear(q_plain, self.uk_t, q_full[:, :, :self.rank])
-        g0 = self.qw + self.width
-        gate = dict(gate=(p[0] if proj.nsplit > 1 else p)[:, g0:g0 + self.heads], gate_nsplit=proj.nsplit,
-                    gate_split_stride=proj.split_stride, gate_per_head=True)
+        g0 = self.qw + (self.width if self.own_kv else 0)
+        gate = {}
+        if self.has_gate:
+            gate = dict(gate=(p[0] if proj.nsplit > 1 else p)[:, g0:g0 + self.heads], gate_nsplit=proj.nsplit,
+                        gate_split_stride=proj.split_stride, gate_per_head=True)
+        opts = dict(gate)                 # what the attention kernels get; the merge of key splits gets the gate only
+        if self.has_sink:
+            opts["sink"] = self.sink
         family = self.kernel_family(cache.page_size)
         vw = self.value_width(cache.page_size)
         lat = ws.get("la_out", (T, self.heads, vw), rt.dtype)                     # sum_j p_j c_j, gated
@@ -122,7 +145,7 @@ class LatentAttention(Mixer):
         part_ml = ws.get("attn_part_ml", (part_rows, self.heads, 2), torch.float32)
         n_small, n_big = meta["n_small"], meta["n_big"]
         common = dict(nq=self.heads, nkv=1, d=self.width, dv=vw, page_size=cache.page_size,
-                      window=self.window or 0, scale=self.scale, shared_kv=True, **gate)
+                      window=self.window or 0, scale=self.scale, shared_kv=True, **opts)
         args = (q_full, cache.storage, lat, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
         if family != "simt":
@@ -132,7 +155,7 @@ class LatentAttention(Mixer):
                 if family == "tc":      # TMA-fed tiles
                     K.attention_tma_ext(*args, meta["items"], n_small, 16, *tail, nq=self.heads, nkv=1, d=self.width,
                                         page_size=cache.page_size, window=self.window or 0, scale=self.scale,
-                                        shared_kv=True, **gate, tok_nsplit=meta["tok_nsplit"], counters=counters,
+                                        shared_kv=True, **opts, tok_nsplit=meta["tok_nsplit"], counters=counters,
                                         status=ctx.status)
                 else:
                     K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common,
@@ -142,7 +165,7 @@ class LatentAttention(Mixer):
                 K.attention_tc_ext(q_full, cache.storage, lat, big_items, n_big, ctx.positions, meta["block_table"],
                                    nq=self.heads, nkv=1, d=self.width, page_size=cache.page_size,
                                    window=self.window or 0, scale=self.scale, status=ctx.status, part_acc=part_acc,
-                                   part_ml=part_ml, tok_part_row=meta["tok_part_row"], shared_kv=True, **gate)
+                                   part_ml=part_ml, tok_part_row=meta["tok_part_row"], shared_kv=True, **opts)
                 if meta.get("big_split"):
                     K.attention_combine(part_acc, part_ml, meta["tok_part_row"], meta["tok_nsplit"], lat,
                                         nq=self.heads, d=vw, **gate)

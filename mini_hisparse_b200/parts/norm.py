@@ -13,7 +13,9 @@ from .spec import ParamSpec, PartSpec
 class RMSNorm(Norm):
     """y = x * rsqrt(mean(x^2) + eps) * weight, computed in float32 from the float32 residual.
 
-    The weight is a plain multiplier (not 1 + w) and there is no bias, as in the reference.
+    The weight is a plain multiplier (not 1 + w) and there is no bias, as in the reference.  With
+    ``offset`` (a number, usually 1) the stored tensor is a deviation around zero and the multiplier is
+    offset + w: the sum is formed once at load, in float32, and the kernels see a plain weight.
     With ``delta`` the kernel first adds it to the residual (and writes the sum back when all
     rows are processed), so the residual add costs no extra pass over memory.
     """
@@ -23,13 +25,16 @@ class RMSNorm(Norm):
         self.width = int(spec["width"])
         self.eps = float(spec["eps"])
         self.weight_name = spec.get("weight_name", "weight")     # "" if the tensor is named by the prefix alone
+        self.offset = float(spec.get("offset", 0.0))
         self.weight = None
 
     def parameters(self):
-        return {self.weight_name: ParamSpec((self.width,), role="vector", init=("normal", 1.0, 0.1))}
+        return {self.weight_name: ParamSpec((self.width,), role="vector", init=("normal", 1.0 - self.offset, 0.1))}
 
     def load(self, tensors):
         self.weight = tensors[self.weight_name]
+        if self.offset:
+            self.weight = self.weight.float() + self.offset
 
     def forward_post(self, x, ctx: StepContext, delta: Product | None, alpha: float = 1.0, keep: float = 0.0,
                      name="x_copy"):

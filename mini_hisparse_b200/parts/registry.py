@@ -49,9 +49,11 @@ POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
+GATES = Registry("gate")
 
 register_mixer: Callable = MIXERS.register
 register_feed_forward: Callable = FEED_FORWARDS.register
 register_norm: Callable = NORMS.register
 register_position: Callable = POSITIONS.register
 register_block: Callable = BLOCKS.register
+register_gate: Callable = GATES.register

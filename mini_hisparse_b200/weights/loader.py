@@ -33,6 +33,11 @@ def _target_dtype(role: str, compute_dtype: torch.dtype) -> torch.dtype:
     return compute_dtype
 
 
+def _fits(found, wanted) -> bool:
+    """A stored shape against a wanted one; a wanted size of -1 takes any size (the part reads it off the tensor)."""
+    return len(found) == len(wanted) and all(w == -1 or int(f) == int(w) for f, w in zip(found, wanted))
+
+
 def check_names(expected: dict, available: dict[str, tuple]) -> None:
     """Raise one WeightError naming missing tensors, unexpected tensors and wrong shapes."""
     missing = [n for n, ps in expected.items() if n not in available and not ps.optional]
@@ -40,7 +45,7 @@ def check_names(expected: dict, available: dict[str, tuple]) -> None:
     wrong = [
         f"{n}: file has {list(available[n])}, model wants {list(ps.shape)}"
         for n, ps in expected.items()
-        if n in available and tuple(available[n]) != tuple(ps.shape)
+        if n in available and not _fits(available[n], ps.shape)
     ]
     if missing or unexpected or wrong:
         lines = ["the checkpoint does not match the model:"]
@@ -94,6 +99,8 @@ def draw(name: str, ps, seed: int, device="cpu", matrix_std: float | None = None
         std = matrix_std
     if kind != "normal":
         raise ValueError(f"unknown init {ps.init!r} for {name}")
+    if any(int(n) < 0 for n in ps.shape):
+        raise ValueError(f"{name}: a size that only a checkpoint gives cannot be drawn at random; name it in the configuration")
     gen = torch.Generator(device=device)
     gen.manual_seed(_tensor_seed(seed, name))
     t = torch.empty(ps.shape, dtype=torch.float32, device=device)
