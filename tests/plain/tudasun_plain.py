@@ -24,9 +24,36 @@ is the oracle of the tests.  Notation: x is the residual stream [T, W]; matrices
 """
 from __future__ import annotations
 
+import json
 import math
+import struct
+from pathlib import Path
 
 import torch
+
+
+# ---- files ---------------------------------------------------------------------------------------
+def read_safetensors(path) -> dict[str, torch.Tensor]:
+    data = Path(path).read_bytes()
+    (n,) = struct.unpack("<Q", data[:8])
+    header = json.loads(data[8:8 + n])
+    kinds = {"BF16": torch.bfloat16, "F32": torch.float32, "I32": torch.int32, "F16": torch.float16}
+    out = {}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = info["data_offsets"]
+        buf = bytearray(data[8 + n + a: 8 + n + b])
+        out[name] = torch.frombuffer(buf, dtype=kinds[info["dtype"]]).reshape(info["shape"]).clone()
+    return out
+
+
+def load_folder(folder, dtype=torch.float64):
+    folder = Path(folder)
+    cfg = json.loads((folder / "config.json").read_text())
+    w = {k: (v.to(dtype) if v.is_floating_point() else v)
+         for k, v in read_safetensors(folder / "model.safetensors").items()}
+    return cfg, w
 
 
 # ---- small functions -------------------------------------------------------------------------------
@@ -214,3 +241,11 @@ def forward(cfg, w, tokens, return_layers=False):
     if cap:
         logits = cap * torch.tanh(logits / cap)
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+def generate(cfg, w, prompt, n):
+    """Greedy continuation of ``prompt`` by n tokens (lowest index wins ties), whole sequence each time."""
+    tokens = list(prompt)
+    for _ in range(n):
+        tokens.append(int(forward(cfg, w, tokens)[-1].argmax()))
+    return tokens[len(prompt):]
