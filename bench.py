@@ -72,7 +72,8 @@ def compare(args) -> int:
     result = measure.compare_architectures(tuple(args.sizes.split(",")), design=design, steps=args.steps,
                                            warmup=args.warmup)
     first = result["sizes"][args.sizes.split(",")[0]]
-    line = {"metric": f"{design.capitalize()} beside Qwen2 at equal size: prefill and decode tokens/s", "unit": "tokens/s",
+    line = {"metric": f"{design.capitalize()} beside {result['beside'].capitalize()} at equal size: prefill and decode tokens/s",
+            "unit": "tokens/s",
             "value": first[design]["decode"]["tokens_per_s"], "n_gpus": 1, "higher_is_better": True,
             "impl": "ours", "dtype": "bf16", "data": "synthetic: seeded random weights and token ids", **result}
     print(json.dumps(line))
@@ -90,9 +91,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex", "dotivik"],
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex", "dotivik", "tudasun"],
                     help="run a serving workload, or the two-architecture comparison, instead of the decode bench")
-    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex or dotivik: which sizes to time")
+    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex, dotivik or tudasun: which sizes to time")
     ap.add_argument("--graph-after", type=int, default=8,
                     help="with --workload: capture a decode graph at the N-th step that asks for it")
     args = ap.parse_args()
@@ -104,7 +105,7 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
-    if args.workload in ("koronex", "dotivik"):
+    if args.workload in ("koronex", "dotivik", "tudasun"):
         if args.steps == 64:
             args.steps = 32
         return compare(args)

@@ -27,9 +27,9 @@ def _top_k(value):
 
 def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="mini_hisparse_b200",
-                                     description="generation on one B200 with hand-written kernels (Qwen2, Koronex and Dotivik model "
-                                                 "folders; --config configs/koronex-demo.json or configs/dotivik-demo.json "
-                                                 "for a demo of those designs)")
+                                     description="generation on one B200 with hand-written kernels (Qwen2, Koronex, Dotivik and Tudasun "
+                                                 "model folders; --config configs/koronex-demo.json, configs/dotivik-demo.json "
+                                                 "or configs/tudasun-demo.json for a demo of those designs)")
     sub = parser.add_subparsers(dest="command", required=True)
     for name in ("demo", "generate", "bench"):
         c = sub.add_parser(name)

@@ -425,6 +425,38 @@ def dotivik_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
                 loop=dict(start=start, stop=start + repeat, times=2))
 
 
+def tudasun_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int,
+                  kv_rank: int = 96, rot_dim: int = 32, side_dim: int = 64) -> dict:
+    """A Tudasun config.json of a real model's sizes: groups of four layers (HGRN2, gated linear attention, latent
+    attention, gated linear attention), the second latent layer of every pair reading the first one's rows.  The
+    recurrent layers have ``heads`` heads with states of head_dim x head_dim; latent layers have ``heads`` heads
+    (head_dim unrotated and rot_dim rotated elements, values head_dim wide) over a cache row of kv_rank + rot_dim =
+    128 numbers.  The first layer's feed-forward is dense (PolyNorm, ``ff`` wide); the others are routed: 14 experts
+    and 2 identity experts in 4 groups of which 2 are kept, 2 a token, each ff / 4 wide, beside a shared expert
+    ff / 2 wide, so that a token's products are as many as in a gated feed-forward ``ff`` wide."""
+    lat = dict(heads=heads, dim=head_dim, rot_dim=rot_dim, vdim=head_dim, kv_rank=kv_rank,
+               scale=(head_dim + rot_dim) ** -0.5, rot=dict(dims=rot_dim, base=10000.0))
+    rec = dict(heads=heads, dim=head_dim, vdim=head_dim)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4), shared=dict(ff=ff // 2),
+               router=dict(experts=14, identity=2, top=2, groups=dict(count=4, keep=2)))
+    out, owner = [], None
+    for i in range(layers):
+        mlp = dict(kind="dense", ff=ff) if i == 0 else moe
+        if i % 4 == 0:
+            out.append(dict(type="hgrn2", mixer=dict(rec), mlp=mlp))
+        elif i % 4 == 2:
+            mixer = dict(lat)
+            if owner is not None:
+                mixer["kv_from"], owner = owner, None
+            else:
+                owner = i
+            out.append(dict(type="latent_attention", mixer=mixer, mlp=mlp))
+        else:
+            out.append(dict(type="gla", mixer=dict(rec, tau=16.0, decay_rank=16), mlp=mlp))
+    return dict(architecture="Tudasun", vocab=vocab, width=width, norm=dict(eps=1e-5), logit_softcap=30.0,
+                token_side=dict(dim=side_dim), layers=out)
+
+
 def qwen2_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int) -> dict:
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=vocab, hidden_size=width,
                 intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads,
@@ -592,18 +624,22 @@ COMPARE_SIZES = {
 }
 
 
-DESIGN_SHAPES = {"koronex": koronex_shape, "dotivik": dotivik_shape}
+DESIGN_SHAPES = {"koronex": koronex_shape, "dotivik": dotivik_shape, "tudasun": tudasun_shape, "qwen2": qwen2_shape}
+# the existing model that a design is set beside: Tudasun beside Koronex, the other design with a recurrent mixer over
+# a float32 state, softmax attention with a sink, layers that read another layer's rows and a per-layer token input
+BESIDE = {"koronex": "qwen2", "dotivik": "qwen2", "tudasun": "koronex"}
 
 
-def compare_architectures(sizes=("2k", "4k"), design: str = "koronex", **kw) -> dict:
-    """``design`` (Koronex or Dotivik) beside the Qwen2 dense model at equal width, heads, feed-forward width
-    and count of layer runs."""
-    out = {"peaks": peaks(), "sizes": {}}
+def compare_architectures(sizes=("2k", "4k"), design: str = "koronex", beside: str | None = None, **kw) -> dict:
+    """``design`` (Koronex, Dotivik or Tudasun) beside another model (``beside``; default: the Qwen2 dense model, for
+    Tudasun Koronex) at equal width, heads, feed-forward width and count of layer runs."""
+    beside = beside or BESIDE[design]
+    out = {"peaks": peaks(), "beside": beside, "sizes": {}}
     for name in sizes:
         shape = COMPARE_SIZES[name]
         out["sizes"][name] = {
             "shape": dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "layers", "vocab"), shape)),
             design: architecture_point(DESIGN_SHAPES[design](*shape), **kw),
-            "qwen2": architecture_point(qwen2_shape(*shape), **kw),
+            beside: architecture_point(DESIGN_SHAPES[beside](*shape), **kw),
         }
     return out
