@@ -189,52 +189,112 @@ scan_kernel(const Rec a, int max_tokens) {
         for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) slot[i] = St[i];
 }
 
-// inclusive running sum of g over the chunk's tokens, one key channel per thread: b[j][i], rows dk + 1 apart
-__device__ __forceinline__ void running_log_decay(const Rec& a, int t0, int n, int h, float* b) {
-    const int dk = a.dk, QW = a.H * dk;
-    for (int i = threadIdx.x; i < dk; i += blockDim.x) {
+// ---- tiles of the chunked route -------------------------------------------------------------------------------
+// A chunk's rows sit in shared memory with their channels rounded up to fours (zeros beyond the head's own), so that
+// every product below runs on float4 loads and register tiles; rows beyond the chunk's tokens are zero as well.
+constexpr int SB = 16;                 // tokens per block of the scores inside a chunk
+__device__ __forceinline__ int round4(int n) { return (n + 3) & ~3; }
+inline size_t round4h(int n) { return (size_t)((n + 3) & ~3); }
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+
+// dst[j][0 .. dpad) = src[t0 + j][col0 .. col0 + d) for j < n, zero elsewhere; C rows, ld apart
+__device__ __forceinline__ void load_rows(float* dst, int ld, const float* __restrict__ src, size_t W, int t0, int n,
+                                          int col0, int d, int dpad, int C) {
+    for (int idx = threadIdx.x; idx < C * dpad; idx += blockDim.x) {
+        const int j = idx / dpad, i = idx - j * dpad;
+        dst[j * ld + i] = (j < n && i < d) ? src[(size_t)(t0 + j) * W + col0 + i] : 0.f;
+    }
+}
+
+// in place: b[j][i] <- b[0][i] + ... + b[j][i], one channel per thread (rows beyond the tokens hold zeros, so they
+// end up with the last token's sum)
+__device__ __forceinline__ void running_sum_rows(float* b, int ld, int dpad, int C) {
+    for (int i = threadIdx.x; i < dpad; i += blockDim.x) {
         float acc = 0.f;
-        for (int j = 0; j < n; ++j) {
-            acc += a.g[(size_t)(t0 + j) * QW + h * dk + i];
-            b[j * (dk + 1) + i] = acc;
+        for (int j = 0; j < C; ++j) {
+            acc += b[j * ld + i];
+            b[j * ld + i] = acc;
         }
     }
 }
 
+__device__ __forceinline__ void fma4(float (&acc)[4], float s, const float4& v) {
+    acc[0] = fmaf(s, v.x, acc[0]);
+    acc[1] = fmaf(s, v.y, acc[1]);
+    acc[2] = fmaf(s, v.z, acc[2]);
+    acc[3] = fmaf(s, v.w, acc[3]);
+}
+
 // ---- chunked (1): every chunk's own contribution U [dk][dv] and its total log decay B [dk] -------------------
 // chunks: {segment, first token, tokens (<= C), index of the chunk in its segment}; U holds dk * dv + dk floats a
-// chunk and head
+// chunk and head.  A thread owns up to 8 x 8 of U: key channels {4 ti .. +3, 64 + 4 ti .. +3} by value channels
+// {4 te .. +3, 64 + 4 te .. +3}, so that a warp's loads of a row are contiguous.
 __global__ void __launch_bounds__(256)
-chunk_state_kernel(const Rec a, const int* __restrict__ chunks, float* __restrict__ U, int C) {
-    extern __shared__ float sm[];
-    const int dk = a.dk, dv = a.dv;
-    float* b = sm;                      // [C][dk + 1]
-    float* ks = b + C * (dk + 1);       // [C][dk + 1]  k_j exp(B - b_j)
-    float* vs = ks + C * (dk + 1);      // [C][dv]
+chunk_state_kernel(const Rec a, const int* __restrict__ chunks, float* __restrict__ U, int C, int vec) {
+    extern __shared__ __align__(16) float sm[];
+    const int dk = a.dk, dv = a.dv, dkp = round4(dk), dvp = round4(dv), LK = dkp + 4;
+    float* b = sm;                      // [C][LK]   running log decay
+    float* ks = b + C * LK;             // [C][LK]   k_j exp(B - b_j)
+    float* vs = ks + C * LK;            // [C][dvp]
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.x, h = blockIdx.y;
     const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
-    const int QW = a.H * dk, VW = a.H * dv;
-    running_log_decay(a, t0, n, h, b);
+    const size_t QW = (size_t)a.H * dk, VW = (size_t)a.H * dv;
+    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C);
+    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C);
+    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
-        const int j = idx / dk, i = idx - j * dk;
-        ks[j * (dk + 1) + i] = a.k[(size_t)(t0 + j) * QW + h * dk + i] * expf(b[(n - 1) * (dk + 1) + i] - b[j * (dk + 1) + i]);
-    }
-    for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
-        const int j = idx / dv, e = idx - j * dv;
-        vs[idx] = a.v[(size_t)(t0 + j) * VW + h * dv + e];
+    running_sum_rows(b, LK, dkp, C);
+    __syncthreads();
+    const float* B = b + (n - 1) * LK;
+    for (int idx = threadIdx.x; idx < n * dkp; idx += blockDim.x) {
+        const int j = idx / dkp, i = idx - j * dkp;
+        ks[j * LK + i] *= expf(B[i] - b[j * LK + i]);
     }
     __syncthreads();
     float* u = U + ((size_t)c * a.H + h) * (dk * dv + dk);
-    for (int idx = threadIdx.x; idx < dk * dv; idx += blockDim.x) {
-        const int i = idx / dv, e = idx - i * dv;
-        float s = 0.f;
-        for (int j = 0; j < n; ++j) s = fmaf(ks[j * (dk + 1) + i], vs[j * dv + e], s);
-        u[idx] = s;
-    }
-    for (int i = threadIdx.x; i < dk; i += blockDim.x) u[dk * dv + i] = b[(n - 1) * (dk + 1) + i];
+    const int ti = threadIdx.x >> 4, te = threadIdx.x & 15, gk = dkp >> 2, ge = dvp >> 2;
+    for (int ia = ti; ia < gk; ia += 32)
+        for (int eb = te; eb < ge; eb += 32) {
+            const int i0 = 4 * ia, i1 = 4 * (ia + 16), e0 = 4 * eb, e1 = 4 * (eb + 16);
+            const bool hi = ia + 16 < gk, he = eb + 16 < ge;
+            float acc[8][2][4];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) acc[r][0][x] = acc[r][1][x] = 0.f;
+            const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int j = 0; j < n; ++j) {
+                const float4 k0 = ld4(ks + j * LK + i0), k1 = hi ? ld4(ks + j * LK + i1) : zero;
+                const float4 v0 = ld4(vs + j * dvp + e0), v1 = he ? ld4(vs + j * dvp + e1) : zero;
+                const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    fma4(acc[r][0], kk[r], v0);
+                    fma4(acc[r][1], kk[r], v1);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                const int i = (r < 4 ? i0 : i1) + (r & 3);
+                if (i >= dk || (r >= 4 && !hi)) continue;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int e = half ? e1 : e0;
+                    if (half && !he) continue;
+                    float* dst = u + (size_t)i * dv + e;
+                    if (vec) {
+                        *reinterpret_cast<float4*>(dst) = make_float4(acc[r][half][0], acc[r][half][1], acc[r][half][2], acc[r][half][3]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            if (e + x < dv) dst[x] = acc[r][half][x];
+                    }
+                }
+            }
+        }
+    for (int i = threadIdx.x; i < dk; i += blockDim.x) u[dk * dv + i] = B[i];
 }
 
 // ---- chunked (2): states at the chunks' starts -----------------------------------------------------------
@@ -271,60 +331,175 @@ chunk_prefix_kernel(const Rec a, const int* __restrict__ seg_chunks, float* __re
 }
 
 // ---- chunked (3): outputs ------------------------------------------------------------------------------
+// o_i = S^T (q_i exp(b_i)) + sum_(j<=i) A[i][j] v_j with A[i][j] = sum_e q_i[e] k_j[e] exp(b_i[e] - b_j[e]).
+// The chunk is cut into blocks of SB tokens.  Inside a block every pair takes its own exponentials.  Between blocks
+// the exponent is split at r = b of the last token before i's block: (q_i exp(b_i - r)) . (k_j exp(r - b_j)), both
+// factors' exponents being sums of g's (<= 0), so the pair's score is one plain dot product and the rows are scaled in
+// place, block after block.  Then [q exp(b) | A] meets [S ; v] in register tiles of 4 tokens (one of every block)
+// by 8 value channels, S staged through the shared memory that b and k no longer need.
 __global__ void __launch_bounds__(256)
-chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __restrict__ U, int C) {
-    extern __shared__ float sm[];
-    const int dk = a.dk, dv = a.dv;
-    float* b = sm;                      // [C][dk + 1]
-    float* qs = b + C * (dk + 1);       // [C][dk + 1]
-    float* ks = qs + C * (dk + 1);      // [C][dk + 1]
-    float* vs = ks + C * (dk + 1);      // [C][dv]
-    float* A = vs + C * dv;             // [C][C + 1]
+chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __restrict__ U, int C, int vec) {
+    extern __shared__ __align__(16) float sm[];
+    const int dk = a.dk, dv = a.dv, dkp = round4(dk), dvp = round4(dv), LK = dkp + 4, LA = C + 4, nb = C / SB;
+    float* b = sm;                      // [C][LK]   running log decay; with ks, later the rows of S
+    float* ks = b + C * LK;             // [C][LK]
+    float* qs = ks + C * LK;            // [C][LK]
+    float* vs = qs + C * LK;            // [C][dvp]
+    float* A = vs + C * dvp;            // [C][LA]
     pdl_launch_dependents();
     pdl_wait();
-    const int c = blockIdx.x, h = blockIdx.y;
+    const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
-    const int QW = a.H * dk, VW = a.H * dv;
-    running_log_decay(a, t0, n, h, b);
-    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
-        const int j = idx / dk, i = idx - j * dk;
-        const size_t src = (size_t)(t0 + j) * QW + h * dk + i;
-        qs[j * (dk + 1) + i] = a.q[src];
-        ks[j * (dk + 1) + i] = a.k[src];
-    }
-    for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
-        const int j = idx / dv, e = idx - j * dv;
-        vs[idx] = a.v[(size_t)(t0 + j) * VW + h * dv + e];
-    }
+    const size_t QW = (size_t)a.H * dk, VW = (size_t)a.H * dv;
+    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C);
+    load_rows(qs, LK, a.q, QW, t0, n, h * dk, dk, dkp, C);
+    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C);
+    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C);
+    for (int idx = tid; idx < C * LA; idx += blockDim.x) A[idx] = 0.f;
     __syncthreads();
-    for (int idx = threadIdx.x; idx < n * n; idx += blockDim.x) {
-        const int i = idx / n, j = idx - i * n;
-        float s = 0.f;
-        if (j <= i) {
-            const float* qi = qs + i * (dk + 1);
-            const float* kj = ks + j * (dk + 1);
-            const float* bi = b + i * (dk + 1);
-            const float* bj = b + j * (dk + 1);
-            for (int e = 0; e < dk; ++e) s = fmaf(qi[e] * kj[e], expf(bi[e] - bj[e]), s);
+    running_sum_rows(b, LK, dkp, C);
+    __syncthreads();
+    // pairs of one block: eight lanes share a pair's channels
+    {
+        const int grp = tid >> 3, l8 = tid & 7, per = SB * (SB + 1) / 2, total = nb * per, g4 = dkp >> 2;
+        for (int p0 = 0; p0 < total; p0 += 32) {
+            const int p = p0 + grp;
+            float s = 0.f;
+            int i = 0, j = 0;
+            if (p < total) {
+                const int I = p / per, rem = p - I * per;
+                int r = 0;
+                while ((r + 1) * (r + 2) / 2 <= rem) ++r;
+                i = I * SB + r;
+                j = I * SB + rem - r * (r + 1) / 2;
+                for (int e4 = l8; e4 < g4; e4 += 8) {
+                    const float4 q4 = ld4(qs + i * LK + 4 * e4), k4 = ld4(ks + j * LK + 4 * e4);
+                    const float4 bi = ld4(b + i * LK + 4 * e4), bj = ld4(b + j * LK + 4 * e4);
+                    s = fmaf(q4.x * k4.x, expf(bi.x - bj.x), s);
+                    s = fmaf(q4.y * k4.y, expf(bi.y - bj.y), s);
+                    s = fmaf(q4.z * k4.z, expf(bi.z - bj.z), s);
+                    s = fmaf(q4.w * k4.w, expf(bi.w - bj.w), s);
+                }
+            }
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (p < total && l8 == 0) A[i * LA + j] = s;
         }
-        A[i * (C + 1) + j] = s;
     }
     __syncthreads();
-    // q_i exp(b_i) in place: what meets the state before the chunk
-    for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
-        const int j = idx / dk, i = idx - j * dk;
-        qs[j * (dk + 1) + i] *= expf(b[j * (dk + 1) + i]);
+    // pairs of different blocks
+    for (int I = 1; I < nb; ++I) {
+        const float* r1 = b + (I * SB - 1) * LK;                 // b of the last token before block I
+        const float* r0 = I > 1 ? b + ((I - 1) * SB - 1) * LK : nullptr;
+        for (int idx = tid; idx < (I + 1) * SB * dkp; idx += blockDim.x) {
+            const int j = idx / dkp, e = idx - j * dkp;
+            if (j >= I * SB) qs[j * LK + e] *= expf(b[j * LK + e] - r1[e]);
+            else if (j >= (I - 1) * SB) ks[j * LK + e] *= expf(r1[e] - b[j * LK + e]);
+            else ks[j * LK + e] *= expf(r1[e] - r0[e]);
+        }
+        __syncthreads();
+        const int ai = I * SB + (tid & 15), jq = tid >> 4;
+        if (jq < 4 * I) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* qrow = qs + ai * LK;
+            const float* krow = ks + 4 * jq * LK;
+            for (int e = 0; e < dkp; e += 4) {
+                const float4 q4 = ld4(qrow + e);
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const float4 k4 = ld4(krow + x * LK + e);
+                    acc[x] = fmaf(q4.x, k4.x, fmaf(q4.y, k4.y, fmaf(q4.z, k4.z, fmaf(q4.w, k4.w, acc[x]))));
+                }
+            }
+            *reinterpret_cast<float4*>(A + ai * LA + 4 * jq) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        }
+        __syncthreads();
     }
-    __syncthreads();
+    // q_i exp(b_i): what meets the state before the chunk (rows of later blocks already carry exp(b_i - r))
+    for (int idx = tid; idx < C * dkp; idx += blockDim.x) {
+        const int j = idx / dkp, e = idx - j * dkp, I = j / SB;
+        qs[j * LK + e] *= expf(I ? b[(I * SB - 1) * LK + e] : b[j * LK + e]);
+    }
     const float* S = U + ((size_t)c * a.H + h) * (dk * dv + dk);
-    for (int idx = threadIdx.x; idx < n * dv; idx += blockDim.x) {
-        const int i = idx / dv, e = idx - i * dv;
-        const float* qi = qs + i * (dk + 1);
-        float o = 0.f;
-        for (int r = 0; r < dk; ++r) o = fmaf(S[r * dv + e], qi[r], o);
-        const float* Ai = A + i * (C + 1);
-        for (int j = 0; j <= i; ++j) o = fmaf(Ai[j], vs[j * dv + e], o);
-        a.out[(size_t)(t0 + i) * VW + h * dv + e] = o;
+    float* Sst = b;                                              // [rows][dvp]
+    const int slab = min(dkp, (2 * C * LK / dvp) & ~3);
+    const int ti = tid >> 4, te = tid & 15, ge = dvp >> 2;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int et = 0; et < ge; et += 32) {
+        const int eb = et + te, e0 = 4 * eb, e1 = 4 * (eb + 16);
+        const bool act = eb < ge, he = eb + 16 < ge;
+        float acc[4][2][4];
+#pragma unroll
+        for (int m = 0; m < 4; ++m)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[m][0][x] = acc[m][1][x] = 0.f;
+        for (int s0 = 0; s0 < dkp; s0 += slab) {
+            const int rows = min(slab, dkp - s0);
+            __syncthreads();
+            for (int idx = tid; idx < rows * dvp; idx += blockDim.x) {
+                const int r = idx / dvp, e = idx - r * dvp;
+                Sst[idx] = (s0 + r < dk && e < dv) ? S[(size_t)(s0 + r) * dv + e] : 0.f;
+            }
+            __syncthreads();
+            if (act)
+                for (int r = 0; r < rows; r += 4) {
+                    float qq[4][4];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const float4 q4 = m < nb ? ld4(qs + (m * SB + ti) * LK + s0 + r) : zero;
+                        qq[m][0] = q4.x; qq[m][1] = q4.y; qq[m][2] = q4.z; qq[m][3] = q4.w;
+                    }
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const float4 s4 = ld4(Sst + (r + x) * dvp + e0), s5 = he ? ld4(Sst + (r + x) * dvp + e1) : zero;
+#pragma unroll
+                        for (int m = 0; m < 4; ++m) {
+                            fma4(acc[m][0], qq[m][x], s4);
+                            fma4(acc[m][1], qq[m][x], s5);
+                        }
+                    }
+                }
+        }
+        if (act) {
+            for (int J = 0; J < nb; ++J)
+                for (int jj = 0; jj < SB; jj += 4) {
+                    float aa[4][4];
+#pragma unroll
+                    for (int m = 0; m < 4; ++m) {
+                        const float4 a4 = (m >= J && m < nb) ? ld4(A + (m * SB + ti) * LA + J * SB + jj) : zero;
+                        aa[m][0] = a4.x; aa[m][1] = a4.y; aa[m][2] = a4.z; aa[m][3] = a4.w;
+                    }
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        const int j = J * SB + jj + x;
+                        const float4 v4 = ld4(vs + j * dvp + e0), v5 = he ? ld4(vs + j * dvp + e1) : zero;
+#pragma unroll
+                        for (int m = 0; m < 4; ++m)
+                            if (m >= J) {
+                                fma4(acc[m][0], aa[m][x], v4);
+                                fma4(acc[m][1], aa[m][x], v5);
+                            }
+                    }
+                }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int i = m * SB + ti;
+                if (m >= nb || i >= n) continue;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    if (half && !he) continue;
+                    float* dst = a.out + (size_t)(t0 + i) * VW + h * dv + (half ? e1 : e0);
+                    if (vec) {
+                        *reinterpret_cast<float4*>(dst) = make_float4(acc[m][half][0], acc[m][half][1], acc[m][half][2], acc[m][half][3]);
+                    } else {
+#pragma unroll
+                        for (int x = 0; x < 4; ++x)
+                            if ((half ? e1 : e0) + x < dv) dst[x] = acc[m][half][x];
+                    }
+                }
+            }
+        }
     }
 }
 
@@ -332,8 +507,14 @@ size_t scan_smem(int dk, int dv, int threads) {
     const int R = threads / dv > 0 ? threads / dv : 1;
     return sizeof(float) * ((size_t)dk * dv + 3 * dk + dv + (size_t)R * dv);
 }
-size_t out_smem(int dk, int dv, int C) { return sizeof(float) * ((size_t)3 * C * (dk + 1) + (size_t)C * dv + (size_t)C * (C + 1)); }
-size_t state_smem(int dk, int dv, int C) { return sizeof(float) * ((size_t)2 * C * (dk + 1) + (size_t)C * dv); }
+size_t out_smem(int dk, int dv, int C) {
+    const size_t LK = round4h(dk) + 4;
+    return sizeof(float) * (3 * C * LK + (size_t)C * round4h(dv) + (size_t)C * (C + 4));
+}
+size_t state_smem(int dk, int dv, int C) {
+    const size_t LK = round4h(dk) + 4;
+    return sizeof(float) * (2 * C * LK + (size_t)C * round4h(dv));
+}
 
 constexpr size_t SMEM_MAX = 200 * 1024;
 
@@ -412,7 +593,11 @@ MHB_EXPORT int mhb_gated_linear_chunked(const float* q, const float* k, const fl
                                         const int* seg_chunks, int num_segs, float* scratch, int C, cudaStream_t stream) {
     if (num_chunks <= 0 || num_segs <= 0) return 0;
     const size_t so = out_smem(dk, dv, C), ss = state_smem(dk, dv, C);
-    if (so > SMEM_MAX || ss > SMEM_MAX) return fail("gated_linear_chunked: chunks of %d tokens of %d x %d do not fit", C, dk, dv);
+    if (C < SB || C > 4 * SB || C % SB) return fail("gated_linear_chunked: chunks of %d tokens (16, 32, 48 or 64)", C);
+    if (so > SMEM_MAX || ss > SMEM_MAX || 2 * C * (round4h(dk) + 4) < 4 * round4h(dv))
+        return fail("gated_linear_chunked: chunks of %d tokens of %d x %d do not fit", C, dk, dv);
+    // whole float4 stores where every row of the outputs starts on 16 bytes
+    const int vec = dk % 4 == 0 && dv % 4 == 0 && (uintptr_t)scratch % 16 == 0 && (uintptr_t)out % 16 == 0;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX) != cudaSuccess ||
@@ -421,12 +606,12 @@ MHB_EXPORT int mhb_gated_linear_chunked(const float* q, const float* k, const fl
         raised = true;
     }
     Rec a = make_rec(q, k, g, v, state, out, tok_seg, seg_slot, positions, T, H, dk, dv, writable);
-    cudaError_t e = launch_kernel(chunk_state_kernel, dim3(num_chunks, H), dim3(256), ss, stream, a, chunks, scratch, C);
+    cudaError_t e = launch_kernel(chunk_state_kernel, dim3(num_chunks, H), dim3(256), ss, stream, a, chunks, scratch, C, vec);
     if (e != cudaSuccess) return fail("gated_linear_chunked (1): %s", cudaGetErrorString(e));
     e = launch_kernel(chunk_prefix_kernel, dim3(num_segs, H, (dk * dv + 255) / 256), dim3(256), 0, stream, a, seg_chunks,
                       scratch);
     if (e != cudaSuccess) return fail("gated_linear_chunked (2): %s", cudaGetErrorString(e));
-    e = launch_kernel(chunk_out_kernel, dim3(num_chunks, H), dim3(256), so, stream, a, chunks, (const float*)scratch, C);
+    e = launch_kernel(chunk_out_kernel, dim3(num_chunks, H), dim3(256), so, stream, a, chunks, (const float*)scratch, C, vec);
     if (e != cudaSuccess) return fail("gated_linear_chunked (3): %s", cudaGetErrorString(e));
     return check_launch("gated_linear_chunked");
 }

@@ -54,8 +54,9 @@ class DecayedStateMixer(Mixer):
         """Tokens per chunk of the chunked route: the largest of 64, 32, 16 whose tiles fit an SM."""
         if not self.chunk:
             self.chunk = 16
+            lk, dvp = (self.dk + 3) // 4 * 4 + 4, (self.dv + 3) // 4 * 4    # rows padded to whole float4s
             for c in (64, 32):
-                if 4 * (3 * c * (self.dk + 1) + c * self.dv + c * (c + 1)) <= SMEM_LIMIT:
+                if 4 * (3 * c * lk + c * dvp + c * (c + 4)) <= SMEM_LIMIT:
                     self.chunk = c
                     break
         return self.chunk
