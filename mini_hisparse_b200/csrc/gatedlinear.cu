@@ -197,12 +197,29 @@ __device__ __forceinline__ int round4(int n) { return (n + 3) & ~3; }
 inline size_t round4h(int n) { return (size_t)((n + 3) & ~3); }
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 
-// dst[j][0 .. dpad) = src[t0 + j][col0 .. col0 + d) for j < n, zero elsewhere; C rows, ld apart
+// 16 bytes from global to shared memory without a register in between; zeros instead where `real` is false
+__device__ __forceinline__ void copy16(float* dst, const float* src, bool real) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    const int bytes = real ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void copies_done() {
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
+}
+
+// dst[j][0 .. dpad) = src[t0 + j][col0 .. col0 + d) for j < n, zero elsewhere; C rows, ld apart, a warp per row.
+// `vec`: d is a multiple of 4 and every row starts on 16 bytes, so that the rows go as asynchronous copies
+// (the caller waits with copies_done() before its barrier).
 __device__ __forceinline__ void load_rows(float* dst, int ld, const float* __restrict__ src, size_t W, int t0, int n,
-                                          int col0, int d, int dpad, int C) {
-    for (int idx = threadIdx.x; idx < C * dpad; idx += blockDim.x) {
-        const int j = idx / dpad, i = idx - j * dpad;
-        dst[j * ld + i] = (j < n && i < d) ? src[(size_t)(t0 + j) * W + col0 + i] : 0.f;
+                                          int col0, int d, int dpad, int C, int vec) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int j = warp; j < C; j += warps) {
+        const float* row = src + (size_t)(t0 + min(j, n - 1)) * W + col0;
+        if (vec) {
+            for (int i = 4 * lane; i < d; i += 128) copy16(dst + j * ld + i, row + i, j < n);
+        } else {
+            for (int i = lane; i < dpad; i += 32) dst[j * ld + i] = (j < n && i < d) ? row[i] : 0.f;
+        }
     }
 }
 
@@ -241,17 +258,16 @@ chunk_state_kernel(const Rec a, const int* __restrict__ chunks, float* __restric
     const int c = blockIdx.x, h = blockIdx.y;
     const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
     const size_t QW = (size_t)a.H * dk, VW = (size_t)a.H * dv;
-    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C);
-    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C);
-    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C);
+    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C, vec);
+    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C, vec);
+    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C, vec);
+    copies_done();
     __syncthreads();
     running_sum_rows(b, LK, dkp, C);
     __syncthreads();
     const float* B = b + (n - 1) * LK;
-    for (int idx = threadIdx.x; idx < n * dkp; idx += blockDim.x) {
-        const int j = idx / dkp, i = idx - j * dkp;
-        ks[j * LK + i] *= expf(B[i] - b[j * LK + i]);
-    }
+    for (int j = threadIdx.x >> 5; j < n; j += blockDim.x >> 5)
+        for (int i = threadIdx.x & 31; i < dkp; i += 32) ks[j * LK + i] *= expf(B[i] - b[j * LK + i]);
     __syncthreads();
     float* u = U + ((size_t)c * a.H + h) * (dk * dv + dk);
     const int ti = threadIdx.x >> 4, te = threadIdx.x & 15, gk = dkp >> 2, ge = dvp >> 2;
@@ -351,11 +367,13 @@ chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __res
     const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int t0 = chunks[4 * c + 1], n = chunks[4 * c + 2];
     const size_t QW = (size_t)a.H * dk, VW = (size_t)a.H * dv;
-    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C);
-    load_rows(qs, LK, a.q, QW, t0, n, h * dk, dk, dkp, C);
-    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C);
-    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C);
+    const int warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+    load_rows(b, LK, a.g, QW, t0, n, h * dk, dk, dkp, C, vec);
+    load_rows(qs, LK, a.q, QW, t0, n, h * dk, dk, dkp, C, vec);
+    load_rows(ks, LK, a.k, QW, t0, n, h * dk, dk, dkp, C, vec);
+    load_rows(vs, dvp, a.v, VW, t0, n, h * dv, dv, dvp, C, vec);
     for (int idx = tid; idx < C * LA; idx += blockDim.x) A[idx] = 0.f;
+    copies_done();
     __syncthreads();
     running_sum_rows(b, LK, dkp, C);
     __syncthreads();
@@ -392,12 +410,12 @@ chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __res
     for (int I = 1; I < nb; ++I) {
         const float* r1 = b + (I * SB - 1) * LK;                 // b of the last token before block I
         const float* r0 = I > 1 ? b + ((I - 1) * SB - 1) * LK : nullptr;
-        for (int idx = tid; idx < (I + 1) * SB * dkp; idx += blockDim.x) {
-            const int j = idx / dkp, e = idx - j * dkp;
-            if (j >= I * SB) qs[j * LK + e] *= expf(b[j * LK + e] - r1[e]);
-            else if (j >= (I - 1) * SB) ks[j * LK + e] *= expf(r1[e] - b[j * LK + e]);
-            else ks[j * LK + e] *= expf(r1[e] - r0[e]);
-        }
+        for (int j = warp; j < (I + 1) * SB; j += warps)
+            for (int e = lane; e < dkp; e += 32) {
+                if (j >= I * SB) qs[j * LK + e] *= expf(b[j * LK + e] - r1[e]);
+                else if (j >= (I - 1) * SB) ks[j * LK + e] *= expf(r1[e] - b[j * LK + e]);
+                else ks[j * LK + e] *= expf(r1[e] - r0[e]);
+            }
         __syncthreads();
         const int ai = I * SB + (tid & 15), jq = tid >> 4;
         if (jq < 4 * I) {
@@ -417,9 +435,9 @@ chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __res
         __syncthreads();
     }
     // q_i exp(b_i): what meets the state before the chunk (rows of later blocks already carry exp(b_i - r))
-    for (int idx = tid; idx < C * dkp; idx += blockDim.x) {
-        const int j = idx / dkp, e = idx - j * dkp, I = j / SB;
-        qs[j * LK + e] *= expf(I ? b[(I * SB - 1) * LK + e] : b[j * LK + e]);
+    for (int j = warp; j < C; j += warps) {
+        const float* bb = j < SB ? b + j * LK : b + (j / SB * SB - 1) * LK;
+        for (int e = lane; e < dkp; e += 32) qs[j * LK + e] *= expf(bb[e]);
     }
     const float* S = U + ((size_t)c * a.H + h) * (dk * dv + dk);
     float* Sst = b;                                              // [rows][dvp]
@@ -437,9 +455,13 @@ chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __res
         for (int s0 = 0; s0 < dkp; s0 += slab) {
             const int rows = min(slab, dkp - s0);
             __syncthreads();
-            for (int idx = tid; idx < rows * dvp; idx += blockDim.x) {
-                const int r = idx / dvp, e = idx - r * dvp;
-                Sst[idx] = (s0 + r < dk && e < dv) ? S[(size_t)(s0 + r) * dv + e] : 0.f;
+            if (vec) {              // whole rows, one after the other
+                for (int idx = 4 * tid; idx < rows * dv; idx += 4 * blockDim.x) copy16(Sst + idx, S + (size_t)s0 * dv + idx, true);
+                copies_done();
+            } else {
+                for (int r = warp; r < rows; r += warps)
+                    for (int e = lane; e < dvp; e += 32)
+                        Sst[r * dvp + e] = (s0 + r < dk && e < dv) ? S[(size_t)(s0 + r) * dv + e] : 0.f;
             }
             __syncthreads();
             if (act)
@@ -597,7 +619,8 @@ MHB_EXPORT int mhb_gated_linear_chunked(const float* q, const float* k, const fl
     if (so > SMEM_MAX || ss > SMEM_MAX || 2 * C * (round4h(dk) + 4) < 4 * round4h(dv))
         return fail("gated_linear_chunked: chunks of %d tokens of %d x %d do not fit", C, dk, dv);
     // whole float4 stores where every row of the outputs starts on 16 bytes
-    const int vec = dk % 4 == 0 && dv % 4 == 0 && (uintptr_t)scratch % 16 == 0 && (uintptr_t)out % 16 == 0;
+    const int vec = dk % 4 == 0 && dv % 4 == 0 &&
+                    ((uintptr_t)scratch | (uintptr_t)out | (uintptr_t)q | (uintptr_t)k | (uintptr_t)g | (uintptr_t)v) % 16 == 0;
     static bool raised = false;
     if (!raised) {
         if (cudaFuncSetAttribute(chunk_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_MAX) != cudaSuccess ||
