@@ -252,16 +252,19 @@ linear_kernel(const XT* __restrict__ x, size_t x_ld, const int* __restrict__ pla
 }
 
 // ---- grouped product, tensor cores (bfloat16) ---------------------------------------------------------------
-// tile: 64 rows x 64 outputs (glu: of gate and of up), K in blocks of 64 staged by cp.async; 4 warps of 16 rows.
-// K and x's row stride are multiples of 8 elements.
-constexpr int GM_N = 64, GM_K = 64, GM_LD = GM_K + 8;
-template <typename OT, bool GLU>
+// tile: 64 rows x 64 outputs (glu: of gate and of up), K in blocks of 64 that cp.async brings in GM_STAGES - 1 blocks
+// ahead of the one the tensor cores work on; 4 warps of 16 rows.  K and x's row stride are multiples of 8 elements.
+// Few rows (decoded tokens) wait on the weights: four stages keep more bytes in flight.  Many rows are bound by the
+// tensor cores and by how many CTAs an SM holds: two stages.
+constexpr int GM_N = 64, GM_K = 64, GM_LD = GM_K + 8, GM_FEW_ROWS = 512;
+constexpr size_t gm_smem(bool glu, int stages) { return (size_t)stages * (TILE_ROWS + (glu ? 2 : 1) * GM_N) * GM_LD * 2; }
+template <typename OT, bool GLU, int GM_STAGES>
 __global__ void __launch_bounds__(128)
 linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_ld, const int* __restrict__ plan, int max_tiles,
                   int pairs, int gather, const __nv_bfloat16* __restrict__ w, OT* __restrict__ out, int N, int K) {
-    __shared__ __align__(16) __nv_bfloat16 xs_m[TILE_ROWS * GM_LD];
-    __shared__ __align__(16) __nv_bfloat16 ws_m[(GLU ? 2 : 1) * GM_N * GM_LD];
+    extern __shared__ __align__(16) unsigned char gm_stages[];       // [GM_STAGES] x {x tile, w tile}
     __shared__ int src[TILE_ROWS];
+    constexpr uint32_t XS_BYTES = TILE_ROWS * GM_LD * 2, STAGE_BYTES = XS_BYTES + (GLU ? 2 : 1) * GM_N * GM_LD * 2;
     pdl_launch_dependents();
     pdl_wait();
     const int tile = blockIdx.x;
@@ -278,8 +281,7 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_ld, const int* _
         src[tid] = r < r1 ? (gather ? row_token[r] : r) : -1;
     }
     __syncthreads();
-    const uint32_t xs = (uint32_t)__cvta_generic_to_shared(xs_m);
-    const uint32_t ws = (uint32_t)__cvta_generic_to_shared(ws_m);
+    const uint32_t stages = (uint32_t)__cvta_generic_to_shared(gm_stages);
     float acc[GM_N / 8][4], acc2[GLU ? GM_N / 8 : 1][4];
 #pragma unroll
     for (int j = 0; j < GM_N / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
@@ -287,7 +289,9 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_ld, const int* _
     for (int j = 0; j < (GLU ? GM_N / 8 : 1); ++j) acc2[j][0] = acc2[j][1] = acc2[j][2] = acc2[j][3] = 0.f;
     const int wrow = warp * 16;
     constexpr int CPR = GM_K / 8;
-    for (int k0 = 0; k0 < K; k0 += GM_K) {
+    auto bring = [&](int kb) {                  // block kb of K into its stage
+        const int k0 = kb * GM_K;
+        const uint32_t xs = stages + (kb % GM_STAGES) * STAGE_BYTES, ws = xs + XS_BYTES;
         for (int c = tid; c < TILE_ROWS * CPR; c += 128) {
             const int r = c / CPR, ch = c - r * CPR;
             const bool live = src[r] >= 0 && k0 + ch * 8 < K;
@@ -301,9 +305,18 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_ld, const int* _
             const __nv_bfloat16* p = live ? we + ((size_t)half * N + n) * K + k0 + ch * 8 : we;
             cp_async16(ws + (r * GM_LD + ch * 8) * 2, p, live ? 16 : 0);
         }
+    };
+    const int nk = (K + GM_K - 1) / GM_K;
+    for (int kb = 0; kb < GM_STAGES - 1; ++kb) {
+        if (kb < nk) bring(kb);
         cp_async_commit();
-        cp_async_wait<0>();
-        __syncthreads();
+    }
+    for (int kb = 0; kb < nk; ++kb) {
+        cp_async_wait<GM_STAGES - 2>();         // block kb has landed (for this thread)
+        __syncthreads();                        // for every thread; and everyone is done with block kb - 1,
+        if (kb + GM_STAGES - 1 < nk) bring(kb + GM_STAGES - 1);      // whose stage the next block takes
+        cp_async_commit();
+        const uint32_t xs = stages + (kb % GM_STAGES) * STAGE_BYTES, ws = xs + XS_BYTES;
 #pragma unroll
         for (int k = 0; k < GM_K; k += 32) {
             uint32_t a0[4], a1[4];
@@ -323,7 +336,6 @@ linear_mma_kernel(const __nv_bfloat16* __restrict__ x, size_t x_ld, const int* _
                 }
             }
         }
-        __syncthreads();
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -411,17 +423,28 @@ MHB_EXPORT int mhb_moe_linear(const void* x, int x_dtype, long long x_ld, const 
         dim3 grid(max_tiles, (N + GM_N - 1) / GM_N);
         const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
         const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+        const bool few = pairs <= GM_FEW_ROWS;
+        if (glu && out_dtype != MHB_BF16) return fail("moe_linear: the gated product writes the compute dtype");
+#define MHB_MOE_MMA(OT, GLU, ST)                                                                                      \
+    do {                                                                                                              \
+        static bool raised = false;                                                                                   \
+        if (!raised) {                                                                                                \
+            if (cudaFuncSetAttribute(linear_mma_kernel<OT, GLU, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                     (int)gm_smem(GLU, ST)) != cudaSuccess)                                           \
+                return fail("moe_linear: cannot raise the shared-memory limit");                                      \
+            raised = true;                                                                                            \
+        }                                                                                                             \
+        e = launch_kernel(linear_mma_kernel<OT, GLU, ST>, grid, dim3(128), gm_smem(GLU, ST), stream, xb, (size_t)x_ld, \
+                          plan, max_tiles, pairs, gather, wb, (OT*)out, N, K);                                        \
+    } while (0)
         if (glu) {
-            if (out_dtype != MHB_BF16) return fail("moe_linear: the gated product writes the compute dtype");
-            e = launch_kernel(linear_mma_kernel<__nv_bfloat16, true>, grid, dim3(128), 0, stream, xb, (size_t)x_ld, plan,
-                              max_tiles, pairs, gather, wb, (__nv_bfloat16*)out, N, K);
+            if (few) MHB_MOE_MMA(__nv_bfloat16, true, 4); else MHB_MOE_MMA(__nv_bfloat16, true, 2);
         } else if (out_dtype == MHB_F32) {
-            e = launch_kernel(linear_mma_kernel<float, false>, grid, dim3(128), 0, stream, xb, (size_t)x_ld, plan,
-                              max_tiles, pairs, gather, wb, (float*)out, N, K);
+            if (few) MHB_MOE_MMA(float, false, 4); else MHB_MOE_MMA(float, false, 2);
         } else {
-            e = launch_kernel(linear_mma_kernel<__nv_bfloat16, false>, grid, dim3(128), 0, stream, xb, (size_t)x_ld, plan,
-                              max_tiles, pairs, gather, wb, (__nv_bfloat16*)out, N, K);
+            if (few) MHB_MOE_MMA(__nv_bfloat16, false, 4); else MHB_MOE_MMA(__nv_bfloat16, false, 2);
         }
+#undef MHB_MOE_MMA
     } else {
         dim3 grid(max_tiles * (TILE_ROWS / GL_T), (N + GL_N - 1) / GL_N);
         if (x_dtype == MHB_F32) {

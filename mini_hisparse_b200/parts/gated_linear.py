@@ -51,14 +51,12 @@ class DecayedStateMixer(Mixer):
         return ChunkPlanner(self._chunk())
 
     def _chunk(self) -> int:
-        """Tokens per chunk of the chunked route: the largest of 64, 32, 16 whose tiles fit an SM."""
+        """Tokens per chunk of the chunked route: 64 where two CTAs' tiles fit an SM side by side, else 32 (shorter
+        chunks cost fewer products inside them and more states), else 16."""
         if not self.chunk:
-            self.chunk = 16
             lk, dvp = (self.dk + 3) // 4 * 4 + 4, (self.dv + 3) // 4 * 4    # rows padded to whole float4s
-            for c in (64, 32):
-                if 4 * (3 * c * lk + c * dvp + c * (c + 4)) <= SMEM_LIMIT:
-                    self.chunk = c
-                    break
+            need = lambda c: 4 * (3 * c * lk + c * dvp + c * (c + 4))
+            self.chunk = 64 if 2 * need(64) <= SMEM_LIMIT else 32 if need(32) <= SMEM_LIMIT else 16
         return self.chunk
 
     def _prepare(self, h, ctx: StepContext, q, k, v, g) -> tuple[Product | None, int]:
