@@ -452,8 +452,8 @@ def tudasun_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
                 owner = i
             out.append(dict(type="latent_attention", mixer=mixer, mlp=mlp))
         else:
-            out.append(dict(type="gla", mixer=dict(rec, tau=16.0, decay_rank=16), mlp=mlp))
-    return dict(architecture="Tudasun", vocab=vocab, width=width, norm=dict(eps=1e-5), logit_softcap=30.0,
+            out.append(dict(type="gla", mixer=dict(rec, tau=8.0, decay_rank=16), mlp=mlp))
+    return dict(architecture="Tudasun", vocab=vocab, width=width, norm=dict(eps=1e-6), logit_softcap=50.0,
                 token_side=dict(dim=side_dim), layers=out)
 
 
