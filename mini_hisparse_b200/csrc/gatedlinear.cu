@@ -195,6 +195,8 @@ scan_kernel(const Rec a, int max_tokens) {
 constexpr int SB = 16;                 // tokens per block of the scores inside a chunk
 __device__ __forceinline__ int round4(int n) { return (n + 3) & ~3; }
 inline size_t round4h(int n) { return (size_t)((n + 3) & ~3); }
+// floats behind the output kernel's q, v and scores: b and k of the chunk, later rows of S (never fewer than four)
+__host__ __device__ inline int stage_floats(int dkp, int dvp, int C) { return max(2 * C * (dkp + 4), 4 * dvp); }
 __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 
 // 16 bytes from global to shared memory without a register in between; zeros instead where `real` is false
@@ -357,11 +359,11 @@ __global__ void __launch_bounds__(256)
 chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __restrict__ U, int C, int vec) {
     extern __shared__ __align__(16) float sm[];
     const int dk = a.dk, dv = a.dv, dkp = round4(dk), dvp = round4(dv), LK = dkp + 4, LA = C + 4, nb = C / SB;
-    float* b = sm;                      // [C][LK]   running log decay; with ks, later the rows of S
-    float* ks = b + C * LK;             // [C][LK]
-    float* qs = ks + C * LK;            // [C][LK]
+    float* qs = sm;                     // [C][LK]
     float* vs = qs + C * LK;            // [C][dvp]
     float* A = vs + C * dvp;            // [C][LA]
+    float* b = A + C * LA;              // [C][LK]   running log decay; from here on, later, rows of S (stage_floats)
+    float* ks = b + C * LK;             // [C][LK]
     pdl_launch_dependents();
     pdl_wait();
     const int c = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
@@ -441,7 +443,7 @@ chunk_out_kernel(const Rec a, const int* __restrict__ chunks, const float* __res
     }
     const float* S = U + ((size_t)c * a.H + h) * (dk * dv + dk);
     float* Sst = b;                                              // [rows][dvp]
-    const int slab = min(dkp, (2 * C * LK / dvp) & ~3);
+    const int slab = min(dkp, (stage_floats(dkp, dvp, C) / dvp) & ~3);      // at least four rows of S
     const int ti = tid >> 4, te = tid & 15, ge = dvp >> 2;
     const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int et = 0; et < ge; et += 32) {
@@ -531,7 +533,8 @@ size_t scan_smem(int dk, int dv, int threads) {
 }
 size_t out_smem(int dk, int dv, int C) {
     const size_t LK = round4h(dk) + 4;
-    return sizeof(float) * (3 * C * LK + (size_t)C * round4h(dv) + (size_t)C * (C + 4));
+    return sizeof(float) * (C * LK + (size_t)C * round4h(dv) + (size_t)C * (C + 4) +
+                            (size_t)stage_floats((int)round4h(dk), (int)round4h(dv), C));
 }
 size_t state_smem(int dk, int dv, int C) {
     const size_t LK = round4h(dk) + 4;
@@ -616,7 +619,7 @@ MHB_EXPORT int mhb_gated_linear_chunked(const float* q, const float* k, const fl
     if (num_chunks <= 0 || num_segs <= 0) return 0;
     const size_t so = out_smem(dk, dv, C), ss = state_smem(dk, dv, C);
     if (C < SB || C > 4 * SB || C % SB) return fail("gated_linear_chunked: chunks of %d tokens (16, 32, 48 or 64)", C);
-    if (so > SMEM_MAX || ss > SMEM_MAX || 2 * C * (round4h(dk) + 4) < 4 * round4h(dv))
+    if (so > SMEM_MAX || ss > SMEM_MAX)
         return fail("gated_linear_chunked: chunks of %d tokens of %d x %d do not fit", C, dk, dv);
     // whole float4 stores where every row of the outputs starts on 16 bytes
     const int vec = dk % 4 == 0 && dv % 4 == 0 &&

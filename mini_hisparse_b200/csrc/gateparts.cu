@@ -7,6 +7,8 @@
 //
 // rms(y) = y / sqrt(mean(y^2) + eps).  Products arrive as float32, possibly as split-K parts that are summed in
 // order; every sum and every norm is float32.
+#include <algorithm>
+
 #include "common.cuh"
 
 using namespace mhb;
@@ -22,8 +24,29 @@ __device__ __forceinline__ float load_parts(const float* p, size_t idx, int nspl
     return v;
 }
 
-template <typename CT>
-__global__ void __launch_bounds__(256)
+// four neighbours at once: the parts' loads of a thread are all in flight before the first addition
+__device__ __forceinline__ float4 load_parts4(const float* p, size_t idx, int nsplit, size_t stride) {
+    float4 v = *reinterpret_cast<const float4*>(p + idx);
+#pragma unroll 8
+    for (int s = 1; s < nsplit; ++s) {
+        const float4 u = *reinterpret_cast<const float4*>(p + idx + (size_t)s * stride);
+        v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+    }
+    return v;
+}
+__device__ __forceinline__ void store4(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float4& v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ float sigmoid_(float z) { return 1.f / (1.f + expf(-z)); }
+
+// VEC: H, the parts' strides and g's row stride are multiples of 4 and every pointer sits on 16 bytes (8 for bfloat16)
+template <typename CT, bool VEC>
+__global__ void __launch_bounds__(1024)
 gated_norm_add_kernel(float* __restrict__ x, const float* __restrict__ d, int dn, size_t ds,
                       const float* __restrict__ g, int gn, size_t gs, int g_ld, const float* __restrict__ bias,
                       const float* __restrict__ w, float eps, CT* __restrict__ copy,
@@ -33,28 +56,59 @@ gated_norm_add_kernel(float* __restrict__ x, const float* __restrict__ d, int dn
     pdl_launch_dependents();
     pdl_wait();
     const size_t r = blockIdx.x;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float y = load_parts(d, r * H + i, dn, ds);
-        if (g) {
-            const float z = load_parts(g, r * g_ld + i, gn, gs) + (bias ? bias[i] : 0.f);
-            y *= 1.f / (1.f + expf(-z));
+    float ss = 0.f, s2 = 0.f;
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+            float4 y = load_parts4(d, r * H + i, dn, ds);
+            if (g) {
+                float4 z = load_parts4(g, r * g_ld + i, gn, gs);
+                if (bias) {
+                    const float4 bb = *reinterpret_cast<const float4*>(bias + i);
+                    z.x += bb.x; z.y += bb.y; z.z += bb.z; z.w += bb.w;
+                }
+                y.x *= sigmoid_(z.x); y.y *= sigmoid_(z.y); y.z *= sigmoid_(z.z); y.w *= sigmoid_(z.w);
+            }
+            store4(row + i, y);
+            ss += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
         }
-        row[i] = y;
-        ss += y * y;
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float y = load_parts(d, r * H + i, dn, ds);
+            if (g) y *= sigmoid_(load_parts(g, r * g_ld + i, gn, gs) + (bias ? bias[i] : 0.f));
+            row[i] = y;
+            ss += y * y;
+        }
     }
     const float rinv = 1.f / sqrtf(block_sum(ss, scratch) / (float)H + eps);
-    float s2 = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = x[r * H + i] + row[i] * rinv * w[i];
-        x[r * H + i] = v;
-        row[i] = v;
-        if (copy) copy[r * H + i] = from_float<CT>(v);
-        s2 += v * v;
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+            const float4 y = *reinterpret_cast<const float4*>(row + i), ww = *reinterpret_cast<const float4*>(w + i);
+            float4 v = *reinterpret_cast<const float4*>(x + r * H + i);
+            v.x += y.x * rinv * ww.x; v.y += y.y * rinv * ww.y; v.z += y.z * rinv * ww.z; v.w += y.w * rinv * ww.w;
+            store4(x + r * H + i, v);
+            store4(row + i, v);
+            if (copy) store4(copy + r * H + i, v);
+            s2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = x[r * H + i] + row[i] * rinv * w[i];
+            x[r * H + i] = v;
+            row[i] = v;
+            if (copy) copy[r * H + i] = from_float<CT>(v);
+            s2 += v * v;
+        }
     }
     if (!next) return;
     const float rinv2 = 1.f / sqrtf(block_sum(s2, scratch) / (float)H + eps2);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) next[r * H + i] = from_float<CT>(row[i] * rinv2 * w2[i]);
+    if (VEC) {
+        for (int i = 4 * threadIdx.x; i < H; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i), ww = *reinterpret_cast<const float4*>(w2 + i);
+            store4(next + r * H + i, make_float4(v.x * rinv2 * ww.x, v.y * rinv2 * ww.y, v.z * rinv2 * ww.z, v.w * rinv2 * ww.w));
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) next[r * H + i] = from_float<CT>(row[i] * rinv2 * w2[i]);
+    }
 }
 
 template <typename OT>
@@ -110,10 +164,22 @@ MHB_EXPORT int mhb_gated_norm_add(float* x, const float* d, int dn, long long ds
                                   float eps2, void* next, int out_dtype, int R, int H, cudaStream_t stream) {
     if (R <= 0) return 0;
     const size_t smem = sizeof(float) * (size_t)H;
+    auto on16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const bool vec = H % 4 == 0 && ds % 4 == 0 && on16(x) && on16(d) && on16(w) && (!g || (gs % 4 == 0 && g_ld % 4 == 0 && on16(g))) &&
+                     (!bias || on16(bias)) && (!copy || on16(copy)) && (!next || (on16(next) && on16(w2)));
+    // a row's elements in fours over up to 1024 threads (few rows, long rows: decoded tokens wait on latency alone)
+    const int per = vec ? 4 : 1, threads = std::min(1024, std::max(128, ((H + per - 1) / per + 31) / 32 * 32));
     MHB_DISPATCH_DTYPE(out_dtype, CT, {
-        if (int rc = raise_smem(gated_norm_add_kernel<CT>, smem, "gated_norm_add")) return rc;
-        cudaError_t e = launch_kernel(gated_norm_add_kernel<CT>, dim3(R), dim3(256), smem, stream, x, d, dn, (size_t)ds, g,
-                                      gn, (size_t)gs, g_ld, bias, w, eps, (CT*)copy, w2, eps2, (CT*)next, H);
+        cudaError_t e;
+        if (vec) {
+            if (int rc = raise_smem(gated_norm_add_kernel<CT, true>, smem, "gated_norm_add")) return rc;
+            e = launch_kernel(gated_norm_add_kernel<CT, true>, dim3(R), dim3(threads), smem, stream, x, d, dn, (size_t)ds, g,
+                              gn, (size_t)gs, g_ld, bias, w, eps, (CT*)copy, w2, eps2, (CT*)next, H);
+        } else {
+            if (int rc = raise_smem(gated_norm_add_kernel<CT, false>, smem, "gated_norm_add")) return rc;
+            e = launch_kernel(gated_norm_add_kernel<CT, false>, dim3(R), dim3(threads), smem, stream, x, d, dn, (size_t)ds, g,
+                              gn, (size_t)gs, g_ld, bias, w, eps, (CT*)copy, w2, eps2, (CT*)next, H);
+        }
         if (e != cudaSuccess) return fail("gated_norm_add: %s", cudaGetErrorString(e));
     });
     return check_launch("gated_norm_add");

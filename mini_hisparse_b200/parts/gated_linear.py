@@ -55,7 +55,7 @@ class DecayedStateMixer(Mixer):
         chunks cost fewer products inside them and more states), else 16."""
         if not self.chunk:
             lk, dvp = (self.dk + 3) // 4 * 4 + 4, (self.dv + 3) // 4 * 4    # rows padded to whole float4s
-            need = lambda c: 4 * (3 * c * lk + c * dvp + c * (c + 4))
+            need = lambda c: 4 * (c * lk + c * dvp + c * (c + 4) + max(2 * c * lk, 4 * dvp))
             self.chunk = 64 if 2 * need(64) <= SMEM_LIMIT else 32 if need(32) <= SMEM_LIMIT else 16
         return self.chunk
 

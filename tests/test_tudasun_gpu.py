@@ -250,7 +250,8 @@ def plain_decayed(q, k, v, decay, S0):
     return torch.stack(out), S
 
 
-@pytest.mark.parametrize("heads,dk,dv,chunk", [(3, 16, 24, 32), (2, 128, 128, 16), (1, 20, 20, 64), (1, 200, 8, 16), (5, 4, 20, 64)])
+@pytest.mark.parametrize("heads,dk,dv,chunk", [(3, 16, 24, 32), (2, 128, 128, 16), (1, 20, 20, 64), (1, 200, 8, 16), (5, 4, 20, 64),
+                                                  (2, 128, 128, 32), (1, 4, 72, 16), (2, 64, 64, 64), (1, 6, 10, 32)])
 def test_the_recurrence_token_by_token_in_chunks_and_plain_agree(heads, dk, dv, chunk):
     """Four segments (a long one from position 0 in a slot that holds another request's state, which must not be
     seen; one that goes on from its slot's state; a single token; a portion of two) through the scan and through
