@@ -49,8 +49,8 @@ __device__ __forceinline__ float load(const Parts& a, size_t t, int col) {
 }
 
 // ---- prep ---------------------------------------------------------------------------------------------
-// grid (T), any block: columns of head-major [H * dk] / [H * dv] rows.  mode 0: the decay's logits are a low-rank
-// product, z = A2 (columns a0 .. a0 + rank of the main product) + bias, taken here in float32.
+// grid (T, slices of the columns), any block: columns of head-major [H * dk] / [H * dv] rows.  mode 0: the decay's
+// logits are a low-rank product, z = A2 (columns a0 .. a0 + rank of the main product) + bias, taken here in float32.
 template <typename WT>
 __global__ void prep_kernel(Parts main, int q0, int k0, int v0, int a0, const WT* __restrict__ a2, int rank,
                             const float* __restrict__ bias, const float* __restrict__ low, float qscale,
@@ -64,7 +64,8 @@ __global__ void prep_kernel(Parts main, int q0, int k0, int v0, int a0, const WT
         for (int r = threadIdx.x; r < rank; r += blockDim.x) lr[r] = load(main, t, a0 + r);
         __syncthreads();
     }
-    for (int i = threadIdx.x; i < QW; i += blockDim.x) {
+    const int span = (max(QW, VW) + gridDim.y - 1) / gridDim.y, c0 = blockIdx.y * span, c1 = c0 + span;
+    for (int i = c0 + threadIdx.x; i < min(QW, c1); i += blockDim.x) {
         const float zq = load(main, t, q0 + i);
         if (mode == 0) {
             float za = 0.f;
@@ -83,7 +84,7 @@ __global__ void prep_kernel(Parts main, int q0, int k0, int v0, int a0, const WT
             g[t * QW + i] = fmaxf(logf(f), G_FLOOR);
         }
     }
-    for (int i = threadIdx.x; i < VW; i += blockDim.x) v[t * VW + i] = load(main, t, v0 + i);
+    for (int i = c0 + threadIdx.x; i < min(VW, c1); i += blockDim.x) v[t * VW + i] = load(main, t, v0 + i);
 }
 
 // ---- behind the recurrence: one norm per head, an optional multiplier ------------------------------------------
@@ -138,7 +139,7 @@ __device__ __forceinline__ void segment_range(const int* tok_seg, int T, int seg
 // ---- token by token ----------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 scan_kernel(const Rec a, int max_tokens) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const int dk = a.dk, dv = a.dv;
     float* St = sm;                     // [dk][dv]
     float* qs = St + dk * dv;           // [dk]
@@ -155,7 +156,13 @@ scan_kernel(const Rec a, int max_tokens) {
     if (t1 <= t0 || (max_tokens > 0 && t1 - t0 > max_tokens)) return;
     float* slot = a.state + ((size_t)a.seg_slot[seg] * a.H + h) * dk * dv;
     const bool fresh = a.positions[t0] == 0;
-    for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) St[i] = fresh ? 0.f : slot[i];
+    const bool by4 = (dk * dv) % 4 == 0 && ((uintptr_t)a.state & 15) == 0;      // a slot then starts on 16 bytes
+    if (by4) {
+        for (int i = 4 * threadIdx.x; i < dk * dv; i += 4 * blockDim.x)
+            *reinterpret_cast<float4*>(St + i) = fresh ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(slot + i);
+    } else {
+        for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) St[i] = fresh ? 0.f : slot[i];
+    }
     const int QW = a.H * dk, VW = a.H * dv;
     for (int t = t0; t < t1; ++t) {
         for (int i = threadIdx.x; i < dk; i += blockDim.x) {
@@ -185,8 +192,14 @@ scan_kernel(const Rec a, int max_tokens) {
         }
     }
     __syncthreads();
-    if (a.writable)
-        for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) slot[i] = St[i];
+    if (a.writable) {
+        if (by4) {
+            for (int i = 4 * threadIdx.x; i < dk * dv; i += 4 * blockDim.x)
+                *reinterpret_cast<float4*>(slot + i) = *reinterpret_cast<const float4*>(St + i);
+        } else {
+            for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) slot[i] = St[i];
+        }
+    }
 }
 
 // ---- tiles of the chunked route -------------------------------------------------------------------------------
@@ -555,7 +568,9 @@ MHB_EXPORT int mhb_gated_linear_prep(const float* main_p, int main_nsplit, long 
     Parts main{main_p, main_nsplit, (size_t)main_stride, main_ld};
     const size_t smem = mode == 0 ? sizeof(float) * rank : 0;
     MHB_DISPATCH_DTYPE(a2_dtype, WT, {
-        cudaError_t e = launch_kernel(prep_kernel<WT>, dim3(T), dim3(256), smem, stream, main, q0, k0, v0, a0,
+        // few tokens: a CTA per 256 columns, so that a decoded token's row is spread over many SMs
+        const int cols = QW > VW ? QW : VW, slices = T >= 64 ? 1 : (cols + 255) / 256;
+        cudaError_t e = launch_kernel(prep_kernel<WT>, dim3(T, slices), dim3(256), smem, stream, main, q0, k0, v0, a0,
                                       (const WT*)a2, rank, bias, low, qscale, inv_tau, mode, q, k, v, g, QW, VW);
         if (e != cudaSuccess) return fail("gated_linear_prep: %s", cudaGetErrorString(e));
     });
