@@ -147,7 +147,8 @@ def close(got, ref, tol, what=""):
 
 
 # ---- the mechanisms alone ---------------------------------------------------------------------------------
-@pytest.mark.parametrize("R,H,nsplit,gated", [(37, 96, 1, True), (5, 100, 3, True), (130, 1000, 2, False), (1, 8, 1, True)])
+@pytest.mark.parametrize("R,H,nsplit,gated", [(37, 96, 1, True), (5, 100, 3, True), (130, 1000, 2, False), (1, 8, 1, True),
+                                              (3, 18, 2, True), (2, 8200, 3, True), (4, 4097, 1, False), (6, 96, 2, True)])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
 def test_gated_normalised_addition_with_the_next_norm(R, H, nsplit, gated, out_dtype):
     """x <- x + rms(d * sigmoid(g + b)) * w over split products, the gate a run of columns of a wider product; the
@@ -157,19 +158,20 @@ def test_gated_normalised_addition_with_the_next_norm(R, H, nsplit, gated, out_d
     g = torch.Generator().manual_seed(R + H)
     x = torch.randn(R, H, generator=g)
     d = torch.randn(nsplit, R, H, generator=g) * 3
-    wide = torch.randn(nsplit, R, H + 7, generator=g)
+    pad, off = (8, 4) if R % 2 == 0 else (7, 3)        # even R: rows that start on 16 bytes (four neighbours a thread)
+    wide = torch.randn(nsplit, R, H + pad, generator=g)
     bias, w, w2 = torch.randn(H, generator=g), 1 + 0.1 * torch.randn(H, generator=g), 1 + 0.1 * torch.randn(H, generator=g)
     eps, eps2 = 1e-5, 1e-3
     y = d.double().sum(0)
     if gated:
-        y = y * torch.sigmoid(wide.double().sum(0)[:, 3:3 + H] + bias.double())
+        y = y * torch.sigmoid(wide.double().sum(0)[:, off:off + H] + bias.double())
     ref = x.double() + P.unit_rms(y, eps) * w.double()
     ref_next = P.unit_rms(ref, eps2) * w2.double()
     xd, dd, wd = x.cuda(), d.cuda(), wide.cuda()
     delta = Parts(dd if nsplit > 1 else dd[0], nsplit)
     gate = None
     if gated:
-        gate = Parts((wd if nsplit > 1 else wd[0])[..., 3:3 + H], nsplit)
+        gate = Parts((wd if nsplit > 1 else wd[0])[..., off:off + H], nsplit)
         gate.split_stride = wd.stride(0) if nsplit > 1 else 0
     copy, nxt = torch.empty(R, H, dtype=out_dtype, device="cuda"), torch.empty(R, H, dtype=out_dtype, device="cuda")
     K.gated_norm_add(xd, delta, w.cuda(), eps, gate=gate, bias=bias.cuda() if gated else None, copy=copy,
@@ -206,15 +208,17 @@ def test_polynorm_and_the_cap(R, F, nsplit):
     close(td, 12.0 * torch.tanh(t.double() / 12.0), 2e-6, "cap")
 
 
-@pytest.mark.parametrize("heads,dk,dv,rank,tau", [(3, 16, 24, 5, 8.0), (1, 20, 20, 1, 1.0), (2, 128, 128, 16, 16.0)])
-@pytest.mark.parametrize("nsplit", [1, 2])
-def test_inputs_of_the_two_recurrences(heads, dk, dv, rank, tau, nsplit):
+@pytest.mark.parametrize("heads,dk,dv,rank,tau", [(3, 16, 24, 5, 8.0), (1, 20, 20, 1, 1.0), (2, 128, 128, 16, 16.0),
+                                                  (5, 64, 96, 4, 2.0), (7, 96, 40, 3, 4.0)])
+@pytest.mark.parametrize("nsplit,T", [(1, 45), (2, 45), (2, 70)])
+def test_inputs_of_the_two_recurrences(heads, dk, dv, rank, tau, nsplit, T):
     """gla: q scaled, k, v, log decay = logsigmoid(A2 (a1 columns) + b) / tau.  hgrn2: q through silu, forget gate
-    above its lower bound, key = 1 - gate, log decay = log gate.  Logits from -60 to 60: nothing overflows."""
+    above its lower bound, key = 1 - gate, log decay = log gate.  Logits from -60 to 60: nothing overflows.  Few
+    tokens spread a row over several CTAs (rows wider than 256, keys wider or narrower than values); many do not."""
     from mini_hisparse_b200.kernels import api as K
 
     g = torch.Generator().manual_seed(heads * dk)
-    T, qw, vw = 45, heads * dk, heads * dv
+    qw, vw = heads * dk, heads * dv
     ld = 2 * qw + 2 * vw + rank + 3
     proj = torch.randn(nsplit, T, ld, generator=g)
     proj[:, 0] *= 30
