@@ -29,6 +29,16 @@
 //   softcap    s <- softcap * tanh(s / softcap) on the scaled score, before the mask and the softmax
 //   shared_kv  the values ARE the first dv elements of the key rows (a latent cache: one row per
 //              position serves as key and as value), so a page holds [nkv][P][kparts * d] and nothing else
+//   prefix     with a window, keys that the window has passed can still be seen in one of two forms, walked
+//              before the item's own key range by the unsplit item or by split 0 only:
+//              pre_kind 1  the first pre_n positions of the sequence stay visible (their own keys and values)
+//              pre_kind 2  every block of pre_n positions that ends at or before position - window is seen as
+//                          ONE key and value (the block's means, kept in the page's tail: after the keys and
+//                          values of its P positions a page holds [nkv][slots][d] pooled keys and
+//                          [nkv][slots][dv] pooled values, slots = ceil(P / pre_n); block b lies in the page
+//                          of its last position, at slot b - floor(page * P / pre_n))
+//   vheads     nkv instead of 1: a query head's weights are applied to the values of EVERY KV head, and the
+//              output row is [nkv][dv] wide (for a mixer that mixes the heads' weights afterwards)
 #include "common.cuh"
 
 using namespace mhb;
@@ -64,6 +74,10 @@ struct AttnArgs {
     int shared_kv;             // values are the head of the key rows
     int gate_per_head;         // the gate has one column per head
     int out_f32;               // `out` is float32 whatever the dtype of q and the cache (a sum is still to come)
+    int pre_kind, pre_n;       // keys seen beyond the window: 0 none, 1 the first pre_n positions, 2 means of blocks of pre_n
+    int pool_slots;            // pooled rows per page and KV head (pre_kind 2)
+    int vheads;                // 1, or nkv: values of every KV head
+    size_t page_extra;         // elements of a page behind its keys and values
 };
 
 __device__ __forceinline__ float gate_of(const AttnArgs& a, int t, int col) {
@@ -78,7 +92,7 @@ template <typename CT, int DPL>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const AttnArgs a) {
     extern __shared__ float smem[];
-    const int d = a.d, dv = a.dv;
+    const int d = a.d, dv = a.dv * a.vheads;      // dv: the width of an output row
     float* q_s = smem;                       // [R_TILE][d]
     float* k_s = q_s + R_TILE * d;           // [KT][d + 1]
     float* v_s = k_s + KT * (d + 1);         // [KT][dv]
@@ -96,9 +110,11 @@ attention_simt_kernel(const AttnArgs a) {
     const int nrows = ntok * nheads;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int k_ld = kparts * d;                                   // a key row of one KV head
-    const int v_ld = a.shared_kv ? k_ld : dv;
+    const int dv1 = a.dv;                                          // one KV head's values
+    const int v_ld = a.shared_kv ? k_ld : dv1;
     const size_t v_plane = a.shared_kv ? 0 : (size_t)a.nkv * a.P * k_ld;
-    const size_t page_elems = (size_t)a.nkv * a.P * k_ld + (a.shared_kv ? 0 : (size_t)a.nkv * a.P * dv);
+    const size_t kv_elems = (size_t)a.nkv * a.P * k_ld + (a.shared_kv ? 0 : (size_t)a.nkv * a.P * dv1);
+    const size_t page_elems = kv_elems + a.page_extra;
     const CT* q = (const CT*)a.q;
     const CT* cache = (const CT*)a.cache;
 
@@ -133,21 +149,47 @@ attention_simt_kernel(const AttnArgs a) {
     }
 
     const int* table = a.block_table + (size_t)seg * a.width;
-    for (int t0 = kv_begin; t0 < kv_end; t0 += KT) {
+    // keys beyond the window (see "prefix" at the top): positions below `beyond` have left the window of the
+    // item's last row, which is the one that sees the most of them
+    int pre_end = 0;
+    if (a.pre_kind && a.window > 0 && split <= 0 && nrows > 0) {
+        const int beyond = a.positions[tok0 + ntok - 1] - a.window + 1;
+        if (beyond > 0) pre_end = a.pre_kind == 1 ? min(a.pre_n, beyond) : beyond / a.pre_n;
+    }
+    for (int phase = pre_end > 0 ? 0 : 1; phase < 2; ++phase) {
+    const int begin = phase ? kv_begin : 0, end = phase ? kv_end : pre_end;
+    const bool pooled = !phase && a.pre_kind == 2;
+    for (int t0 = begin; t0 < end; t0 += KT) {
         // load KT keys and values: warp w takes keys w*8 .. w*8+7, lanes run along d
         for (int j = warp * (KT / WARPS); j < (warp + 1) * (KT / WARPS); ++j) {
             const int kp = t0 + j;
-            int page = -1;
-            if (kp < kv_end) {
-                page = table[kp / a.P];
+            int page = -1, slot = 0;
+            if (kp < end) {
+                const int pg = pooled ? (kp * a.pre_n + a.pre_n - 1) / a.P : kp / a.P;
+                slot = pooled ? kp - (int)(((long long)pg * a.P) / a.pre_n) : kp - pg * a.P;
+                page = table[pg];
                 if (page >= a.num_pages) page = -1;
             }
             if (page >= 0) {
                 const size_t pbase = (size_t)page * page_elems;
-                const size_t off = pbase + ((size_t)kvh * a.P + kp % a.P) * k_ld + map * d;
-                const size_t voff = pbase + v_plane + ((size_t)kvh * a.P + kp % a.P) * v_ld;
-                for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
-                for (int e = lane; e < dv; e += 32) v_s[j * dv + e] = to_float(cache[voff + e]);
+                if (pooled) {
+                    const size_t off = pbase + kv_elems + ((size_t)kvh * a.pool_slots + slot) * d;
+                    for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
+                    for (int c = 0; c < a.vheads; ++c) {
+                        const int vh = a.vheads > 1 ? c : kvh;
+                        const size_t voff = pbase + kv_elems + (size_t)a.nkv * a.pool_slots * d +
+                                            ((size_t)vh * a.pool_slots + slot) * dv1;
+                        for (int e = lane; e < dv1; e += 32) v_s[j * dv + c * dv1 + e] = to_float(cache[voff + e]);
+                    }
+                } else {
+                    const size_t off = pbase + ((size_t)kvh * a.P + slot) * k_ld + map * d;
+                    for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
+                    for (int c = 0; c < a.vheads; ++c) {
+                        const int vh = a.vheads > 1 ? c : kvh;
+                        const size_t voff = pbase + v_plane + ((size_t)vh * a.P + slot) * v_ld;
+                        for (int e = lane; e < dv1; e += 32) v_s[j * dv + c * dv1 + e] = to_float(cache[voff + e]);
+                    }
+                }
             } else {
                 for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = 0.f;
                 for (int e = lane; e < dv; e += 32) v_s[j * dv + e] = 0.f;
@@ -166,7 +208,10 @@ attention_simt_kernel(const AttnArgs a) {
             for (int e = 0; e < d; ++e) s = fmaf(qr[e], kr[e], s);
             s *= a.scale;
             if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
-            const bool valid = kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
+            bool valid;
+            if (phase) valid = kp < end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
+            else if (pooled) valid = kp < end && qp - a.window + 1 > 0 && kp < (qp - a.window + 1) / a.pre_n;
+            else valid = kp < end && kp <= qp - a.window;
             if (!valid) s = -INFINITY;
             const float m_new = fmaxf(m[rs], warp_max(s));
             float p = 0.f, alpha = 1.f;
@@ -188,6 +233,7 @@ attention_simt_kernel(const AttnArgs a) {
             }
         }
         __syncthreads();
+    }
     }
 
 #pragma unroll
@@ -268,9 +314,10 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_acc,
 
 template <typename CT>
 int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
-    int dpl = (a.dv + 31) / 32;
+    const int dvt = a.dv * a.vheads;
+    int dpl = (dvt + 31) / 32;
     if (dpl > 8) dpl = dpl <= 12 ? 12 : 16;      // wide values: accumulators for 384 or 512 elements per row
-    const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * a.dv);
+    const size_t smem = sizeof(float) * ((size_t)R_TILE * a.d + (size_t)KT * (a.d + 1) + (size_t)KT * dvt);
     dim3 grid(max_items, a.nkv * a.kparts);
 #define MHB_ATTN_CASE(N)                                                                        \
     case N: {                                                                                   \
@@ -288,7 +335,7 @@ int launch_attention(const AttnArgs& a, int max_items, cudaStream_t stream) {
         MHB_ATTN_CASE(1) MHB_ATTN_CASE(2) MHB_ATTN_CASE(3) MHB_ATTN_CASE(4)
         MHB_ATTN_CASE(5) MHB_ATTN_CASE(6) MHB_ATTN_CASE(7) MHB_ATTN_CASE(8)
         MHB_ATTN_CASE(12) MHB_ATTN_CASE(16)
-        default: return fail("attention: a value width of %d is larger than 512", a.dv);
+        default: return fail("attention: a value width of %d is larger than 512", dvt);
     }
 #undef MHB_ATTN_CASE
     return check_launch("attention_simt");
@@ -310,20 +357,24 @@ MHB_EXPORT int mhb_attention_simt(const void* q, const void* cache, void* out, i
     a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.dv = d; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
     a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
+    a.pre_kind = 0; a.pre_n = 0; a.pool_slots = 0; a.vheads = 1; a.page_extra = 0;
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
 }
 
 // The same with the options: values dv wide, a sink per query head, a gate on the output.
-MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* out, int dtype,
+namespace {
+int attention_simt_options(const void* q, const void* cache, void* out, int dtype,
                                       float* part_acc, float* part_ml, const int* items, int num_items,
                                       int max_items, const int* positions, const int* block_table,
                                       int width, const int* tok_part_row, int nq, int nkv, int d, int dv, int P,
                                       int num_pages, int window, float scale, const float* sink,
                                       const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
                                       int kparts, float softcap, int shared_kv, int gate_per_head, int out_f32,
-                                      cudaStream_t stream) {
+                                      int pre_kind, int pre_n, int all_values, cudaStream_t stream) {
     if (max_items <= 0) return 0;
+    if (pre_kind < 0 || pre_kind > 2 || (pre_kind && pre_n < 1)) return fail("attention: keys beyond the window of kind %d over %d positions", pre_kind, pre_n);
+    if ((pre_kind || all_values) && (kparts != 1 || shared_kv)) return fail("attention: keys beyond the window and values of every KV head go with plain key and value rows only");
     if (kparts < 1 || nq % (nkv > 0 ? nkv * kparts : 1)) return fail("attention: %d query heads over %d KV heads with %d score maps each", nq, nkv, kparts);
     if ((long long)nkv * kparts > 65535) return fail("attention: too many KV heads");
     if (shared_kv && dv > kparts * d) return fail("attention: values %d wide cannot be the head of key rows %d wide", dv, kparts * d);
@@ -339,8 +390,41 @@ MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* ou
     a.gate_split_stride = (size_t)gate_split_stride;
     a.kparts = kparts; a.softcap = softcap; a.shared_kv = shared_kv; a.gate_per_head = gate_per_head;
     a.out_f32 = out_f32;
+    a.pre_kind = pre_kind; a.pre_n = pre_n; a.vheads = all_values ? nkv : 1;
+    a.pool_slots = pre_kind == 2 ? (P + pre_n - 1) / pre_n : 0;
+    a.page_extra = (size_t)nkv * a.pool_slots * (d + dv);
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
+}
+}  // namespace
+
+MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* out, int dtype,
+                                      float* part_acc, float* part_ml, const int* items, int num_items,
+                                      int max_items, const int* positions, const int* block_table,
+                                      int width, const int* tok_part_row, int nq, int nkv, int d, int dv, int P,
+                                      int num_pages, int window, float scale, const float* sink,
+                                      const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
+                                      int kparts, float softcap, int shared_kv, int gate_per_head, int out_f32,
+                                      cudaStream_t stream) {
+    return attention_simt_options(q, cache, out, dtype, part_acc, part_ml, items, num_items, max_items, positions,
+                                  block_table, width, tok_part_row, nq, nkv, d, dv, P, num_pages, window, scale, sink,
+                                  gate, gate_nsplit, gate_split_stride, gate_ld, kparts, softcap, shared_kv,
+                                  gate_per_head, out_f32, 0, 0, 0, stream);
+}
+
+// The same with keys that stay visible beyond the window (pre_kind, pre_n) and with the values of every KV head
+// under each query head's weights (all_values): see "prefix" and "vheads" at the top.
+MHB_EXPORT int mhb_attention_simt_masked(const void* q, const void* cache, void* out, int dtype,
+                                         float* part_acc, float* part_ml, const int* items, int num_items,
+                                         int max_items, const int* positions, const int* block_table,
+                                         int width, const int* tok_part_row, int nq, int nkv, int d, int dv, int P,
+                                         int num_pages, int window, float scale, const float* sink,
+                                         const float* gate, int gate_nsplit, long long gate_split_stride, int gate_ld,
+                                         int out_f32, int pre_kind, int pre_n, int all_values, cudaStream_t stream) {
+    return attention_simt_options(q, cache, out, dtype, part_acc, part_ml, items, num_items, max_items, positions,
+                                  block_table, width, tok_part_row, nq, nkv, d, dv, P, num_pages, window, scale, sink,
+                                  gate, gate_nsplit, gate_split_stride, gate_ld, 1, 0.f, 0, 0, out_f32, pre_kind,
+                                  pre_n, all_values, stream);
 }
 
 // every > 0: token t has `every` parts in the rows t * every ... of the partial buffers (tok_part_row and

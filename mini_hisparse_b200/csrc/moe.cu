@@ -34,7 +34,8 @@ __device__ __forceinline__ float load_parts(const float* p, size_t idx, int nspl
 // one warp per token; shared memory: per warp n softmax values, n choice scores, `groups` group scores
 __global__ void __launch_bounds__(128)
 route_kernel(const float* __restrict__ logits, int nsplit, size_t stride, int ld, const float* __restrict__ correction,
-             int* __restrict__ chosen, float* __restrict__ weights, int T, int n, int top, int groups, int keep) {
+             int* __restrict__ chosen, float* __restrict__ weights, int T, int n, int top, int groups, int keep,
+             const float* __restrict__ bias) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -46,7 +47,7 @@ route_kernel(const float* __restrict__ logits, int nsplit, size_t stride, int ld
     float* gs = c + n;
     float mx = -INFINITY;
     for (int i = lane; i < n; i += 32) {
-        const float z = load_parts(logits, (size_t)t * ld + i, nsplit, stride);
+        const float z = load_parts(logits, (size_t)t * ld + i, nsplit, stride) + (bias ? bias[i] : 0.f);
         s[i] = z;
         mx = fmaxf(mx, z);
     }
@@ -60,7 +61,7 @@ route_kernel(const float* __restrict__ logits, int nsplit, size_t stride, int ld
     sum = warp_sum(sum);
     for (int i = lane; i < n; i += 32) {
         s[i] = s[i] / sum;
-        c[i] = s[i] + correction[i];
+        c[i] = s[i] + (correction ? correction[i] : 0.f);
     }
     __syncwarp();
     if (groups > 1 && keep < groups) {
@@ -385,9 +386,11 @@ combine_kernel(const float* __restrict__ y, const int* __restrict__ plan, int ma
 
 MHB_EXPORT int mhb_moe_tile_rows() { return TILE_ROWS; }
 
-MHB_EXPORT int mhb_moe_route(const float* logits, int nsplit, long long stride, int ld, const float* correction,
-                             int* chosen, float* weights, int T, int n, int top, int groups, int keep,
-                             cudaStream_t stream) {
+// bias (or null): added to the logits before the softmax; correction may be null too (no correction).  With both
+// null groups the choice is by the logits themselves and the weights are the softmax over the chosen logits.
+MHB_EXPORT int mhb_moe_route_biased(const float* logits, int nsplit, long long stride, int ld, const float* bias,
+                                    const float* correction, int* chosen, float* weights, int T, int n, int top,
+                                    int groups, int keep, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (top < 1 || top > n) return fail("moe_route: %d picks among %d outputs", top, n);
     if (groups < 1 || n % groups || keep < 1 || keep > groups)
@@ -397,9 +400,16 @@ MHB_EXPORT int mhb_moe_route(const float* logits, int nsplit, long long stride, 
     const size_t smem = sizeof(float) * warps * (2 * (size_t)n + groups);
     if (smem > 48 * 1024) return fail("moe_route: %d router outputs are more than the kernel holds", n);
     cudaError_t e = launch_kernel(route_kernel, dim3((T + warps - 1) / warps), dim3(32 * warps), smem, stream, logits,
-                                  nsplit, (size_t)stride, ld, correction, chosen, weights, T, n, top, groups, keep);
+                                  nsplit, (size_t)stride, ld, correction, chosen, weights, T, n, top, groups, keep, bias);
     if (e != cudaSuccess) return fail("moe_route: %s", cudaGetErrorString(e));
     return check_launch("moe_route");
+}
+
+MHB_EXPORT int mhb_moe_route(const float* logits, int nsplit, long long stride, int ld, const float* correction,
+                             int* chosen, float* weights, int T, int n, int top, int groups, int keep,
+                             cudaStream_t stream) {
+    return mhb_moe_route_biased(logits, nsplit, stride, ld, nullptr, correction, chosen, weights, T, n, top, groups,
+                                keep, stream);
 }
 
 MHB_EXPORT int mhb_moe_plan(const int* chosen, int pairs, int top, int experts, int max_tiles, int* plan,

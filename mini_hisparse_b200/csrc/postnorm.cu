@@ -220,8 +220,9 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, int nsp
                                           const int* __restrict__ tok_seg, const int* __restrict__ block_table,
                                           int table_width, const float* __restrict__ inv_freq, int rdim,
                                           QT* __restrict__ q_out, CT* __restrict__ cache, int nq, int nkv, int dk,
-                                          int dv, int P, int num_pages, int has_kv, int* __restrict__ status) {
-    extern __shared__ float sh[];            // q row, k row, cos, sin
+                                          int dv, int P, int num_pages, int has_kv, int* __restrict__ status,
+                                          int per_head, float v_eps, size_t page_extra) {
+    extern __shared__ float sh[];            // q row, k row, cos, sin (and the v row, if it is normalised)
     __shared__ float scratch[33];
     pdl_launch_dependents();
     pdl_wait();
@@ -246,13 +247,42 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, int nsp
         cs[i] = c;
         sn[i] = s;
     }
-    const float tq = block_sum(ssq, scratch);
-    const float tk = block_sum(ssk, scratch);
-    const float rq = 1.f / sqrtf(tq / (float)qw + eps);
-    const float rk = kw ? 1.f / sqrtf(tk / (float)kw + eps) : 0.f;
-    for (int i = threadIdx.x; i < qw + kw; i += blockDim.x)
-        sh[i] = i < qw ? sh[i] * rq * q_weight[i] : sh[i] * rk * k_weight[i - qw];
+    float* vs = sn + rhalf;                  // [vw], only with v_eps > 0
+    if (v_eps > 0.f)
+        for (int i = threadIdx.x; i < vw; i += blockDim.x) vs[i] = load_parts(qkv, base + qw + kw + i, nsplit, split_stride);
+    if (per_head) {
+        // one norm per head over its dk elements, the weight [dk] shared by the heads: a warp per head
+        __syncthreads();
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+        for (int head = warp; head < (qw + kw) / dk; head += nwarps) {
+            float* row = sh + head * dk;
+            const float* w = head < nq ? q_weight : k_weight;
+            float ss = 0.f;
+            for (int e = lane; e < dk; e += 32) ss += row[e] * row[e];
+            const float r = 1.f / sqrtf(warp_sum(ss) / (float)dk + eps);
+            for (int e = lane; e < dk; e += 32) row[e] = row[e] * r * w[e];
+        }
+    } else {
+        const float tq = block_sum(ssq, scratch);
+        const float tk = block_sum(ssk, scratch);
+        const float rq = 1.f / sqrtf(tq / (float)qw + eps);
+        const float rk = kw ? 1.f / sqrtf(tk / (float)kw + eps) : 0.f;
+        for (int i = threadIdx.x; i < qw + kw; i += blockDim.x)
+            sh[i] = i < qw ? sh[i] * rq * q_weight[i] : sh[i] * rk * k_weight[i - qw];
+    }
     __syncthreads();
+    if (v_eps > 0.f) {
+        // every head's value divided by its own root mean square (no weight): a warp per head
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+        for (int head = warp; head < (has_kv ? nkv : 0); head += nwarps) {
+            float* row = vs + head * dv;
+            float ss = 0.f;
+            for (int e = lane; e < dv; e += 32) ss += row[e] * row[e];
+            const float r = 1.f / sqrtf(warp_sum(ss) / (float)dv + v_eps);
+            for (int e = lane; e < dv; e += 32) row[e] *= r;
+        }
+        __syncthreads();
+    }
     CT* page_k = nullptr;
     CT* page_v = nullptr;
     const int within = pos % P;
@@ -261,7 +291,7 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, int nsp
         if (page < 0 || page >= num_pages) {          // never write outside the pool
             if (threadIdx.x == 0 && status) atomicOr(status, 2);
         } else {
-            page_k = cache + (size_t)page * nkv * P * (dk + dv);
+            page_k = cache + (size_t)page * ((size_t)nkv * P * (dk + dv) + page_extra);
             page_v = page_k + (size_t)nkv * P * dk;
         }
     }
@@ -289,7 +319,7 @@ __global__ void qknorm_rope_append_kernel(const float* __restrict__ qkv, int nsp
         for (int i = threadIdx.x; i < vw; i += blockDim.x) {
             const int g = i / dv, e = i - g * dv;
             page_v[((size_t)g * P + within) * dv + e] =
-                from_float<CT>(load_parts(qkv, base + qw + kw + i, nsplit, split_stride));
+                from_float<CT>(v_eps > 0.f ? vs[i] : load_parts(qkv, base + qw + kw + i, nsplit, split_stride));
         }
     }
 }
@@ -385,22 +415,37 @@ MHB_EXPORT int mhb_gated_rmsnorm(const float* o, const float* gate, int gate_nsp
     return check_launch("gated_rmsnorm");
 }
 
+// per_head: the two norms run over each head alone, with weights [dk] that the heads share, instead of over the whole
+// projections.  v_eps > 0: every head's value is divided by its root mean square (with that eps) before it is stored.
+// page_extra: elements of a page behind its keys and values (left alone here).
+MHB_EXPORT int mhb_qknorm_rope_append_opts(const float* qkv, int nsplit, long long split_stride, int ld,
+                                      const float* q_weight, const float* k_weight, float eps, const int* positions,
+                                      const int* tok_seg, const int* block_table, int table_width,
+                                      const float* inv_freq, int rdim, void* q_out, void* cache, int dtype, int T,
+                                      int nq, int nkv, int dk, int dv, int P, int num_pages, int has_kv, int* status,
+                                      int per_head, float v_eps, long long page_extra, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rdim < 0 || rdim > dk || (rdim & 1)) return fail("qknorm_rope_append: %d rotated elements of a head of %d", rdim, dk);
+    const int qw = nq * dk, kw = has_kv ? nkv * dk : 0;
+    const size_t smem = sizeof(float) * ((size_t)qw + kw + rdim + (v_eps > 0.f && has_kv ? (size_t)nkv * dv : 0));
+    MHB_DISPATCH_DTYPE(dtype, CT, {
+        auto kern = qknorm_rope_append_kernel<CT, CT>;
+        if (allow_smem(kern, smem, "qknorm_rope_append")) return -1;
+        launch_kernel(kern, dim3(T), dim3(row_threads(qw + kw)), smem, stream, qkv, nsplit, (size_t)split_stride, ld,
+                      q_weight, k_weight, eps, positions, tok_seg, block_table, table_width, inv_freq, rdim,
+                      (CT*)q_out, (CT*)cache, nq, nkv, dk, dv, P, num_pages, has_kv, status, per_head, v_eps,
+                      (size_t)page_extra);
+    });
+    return check_launch("qknorm_rope_append");
+}
+
 MHB_EXPORT int mhb_qknorm_rope_append(const float* qkv, int nsplit, long long split_stride, int ld,
                                       const float* q_weight, const float* k_weight, float eps, const int* positions,
                                       const int* tok_seg, const int* block_table, int table_width,
                                       const float* inv_freq, int rdim, void* q_out, void* cache, int dtype, int T,
                                       int nq, int nkv, int dk, int dv, int P, int num_pages, int has_kv, int* status,
                                       cudaStream_t stream) {
-    if (T <= 0) return 0;
-    if (rdim < 0 || rdim > dk || (rdim & 1)) return fail("qknorm_rope_append: %d rotated elements of a head of %d", rdim, dk);
-    const int qw = nq * dk, kw = has_kv ? nkv * dk : 0;
-    const size_t smem = sizeof(float) * ((size_t)qw + kw + rdim);
-    MHB_DISPATCH_DTYPE(dtype, CT, {
-        auto kern = qknorm_rope_append_kernel<CT, CT>;
-        if (allow_smem(kern, smem, "qknorm_rope_append")) return -1;
-        launch_kernel(kern, dim3(T), dim3(row_threads(qw + kw)), smem, stream, qkv, nsplit, (size_t)split_stride, ld,
-                      q_weight, k_weight, eps, positions, tok_seg, block_table, table_width, inv_freq, rdim,
-                      (CT*)q_out, (CT*)cache, nq, nkv, dk, dv, P, num_pages, has_kv, status);
-    });
-    return check_launch("qknorm_rope_append");
+    return mhb_qknorm_rope_append_opts(qkv, nsplit, split_stride, ld, q_weight, k_weight, eps, positions, tok_seg,
+                                       block_table, table_width, inv_freq, rdim, q_out, cache, dtype, T, nq, nkv, dk, dv,
+                                       P, num_pages, has_kv, status, 0, 0.f, 0, stream);
 }

@@ -165,12 +165,15 @@ def gated_rmsnorm(o, weight, eps, out, gate=None, gate_nsplit=1, gate_split_stri
 
 
 def qknorm_rope_append(qkv, q_weight, k_weight, eps, positions, tok_seg, block_table, inv_freq, rotary_dim, q_out,
-                       cache, *, nq, nkv, dk, dv, page_size, has_kv=True, nsplit=1, split_stride=0, status=None):
+                       cache, *, nq, nkv, dk, dv, page_size, has_kv=True, nsplit=1, split_stride=0, status=None,
+                       per_head=False, v_eps=0.0, page_extra=0):
     """RMS norm over the whole q projection and over the whole k projection, rotation of the first
     ``rotary_dim`` elements of every head (pairs (i, i + rotary_dim/2)), q to ``q_out`` [T, nq dk], k and v
     into the pages of ``cache`` (one layer's pool; a page holds [nkv][P][dk] keys then [nkv][P][dv] values).
     ``qkv`` float32 [.., T, ld] holds [q | k | v | ...] per row; with ``has_kv`` False it holds [q | ...]
-    and nothing is appended."""
+    and nothing is appended.  ``per_head``: the norms run over each head alone with weights [dk] shared by the
+    heads.  ``v_eps`` > 0: every head's value is divided by its root mean square before it is stored.
+    ``page_extra``: elements of a page behind its keys and values, which this kernel leaves alone."""
     lib = build.load("postnorm")
     T = q_out.shape[0]
     if qkv.dtype != torch.float32 or qkv.stride(-1) != 1:
@@ -179,12 +182,13 @@ def qknorm_rope_append(qkv, q_weight, k_weight, eps, positions, tok_seg, block_t
         raise KernelError("qknorm_rope_append: the pool must be contiguous and of the activations' dtype")
     if rotary_dim and (inv_freq is None or inv_freq.numel() != rotary_dim // 2):
         raise KernelError(f"qknorm_rope_append: {rotary_dim} rotated elements need {rotary_dim // 2} frequencies")
-    _check(lib, lib.mhb_qknorm_rope_append(
+    _check(lib, lib.mhb_qknorm_rope_append_opts(
         _ptr(qkv), c_int(nsplit), c_longlong(split_stride), c_int(qkv.stride(-2)), _ptr(q_weight), _ptr(k_weight),
         c_float(eps), _ptr(positions), _ptr(tok_seg), _ptr(block_table), c_int(block_table.shape[-1]),
         _ptr(inv_freq), c_int(rotary_dim), _ptr(q_out), _ptr(cache if has_kv else None), c_int(dtype_code(q_out.dtype)),
         c_int(T), c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page_size),
-        c_int(cache.shape[0] if has_kv else 0), c_int(1 if has_kv else 0), _ptr(status), _stream()),
+        c_int(cache.shape[0] if has_kv else 0), c_int(1 if has_kv else 0), _ptr(status), c_int(1 if per_head else 0),
+        c_float(v_eps or 0.0), c_longlong(page_extra), _stream()),
         "qknorm_rope_append")
 
 
@@ -450,17 +454,36 @@ def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
                    block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, dv=None,
                    sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, kparts=1, softcap=0.0,
-                   shared_kv=False, gate_per_head=False):
+                   shared_kv=False, gate_per_head=False, keep_first=0, pool=0, all_values=False):
     """CUDA-core attention over the items of a plan.  Options: ``dv`` values of another width than the
     keys (a page then holds the keys of all KV heads followed by their values), ``sink`` float32 [nq]
     (one extra term exp(sink_h) in the softmax's denominator), ``gate`` (the output is multiplied by its
     sigmoid; columns of a float32 product; ``gate_per_head``: one column per head), ``kparts`` score maps
     per KV head (its key row holds kparts keys side by side; ``nq`` counts every map of every head),
     ``softcap`` (s <- softcap tanh(s / softcap)), ``shared_kv`` (the values are the first dv elements of
-    the key rows, and a page holds nothing but those rows)."""
+    the key rows, and a page holds nothing but those rows).  With a window: ``keep_first`` positions at the
+    start of a sequence stay visible, or (``pool``) every block of ``pool`` positions that the window has passed
+    wholly is seen as one key and value, its means, from the tail of its page (csrc/maskparts.cu).
+    ``all_values``: every query head's weights are applied to the values of all KV heads, and ``out`` is
+    [T, nq, nkv * dv]."""
     lib = build.load("attention_simt")
     if scale is None:
         scale = float(d) ** -0.5
+    if keep_first or pool or all_values:
+        if keep_first and pool:
+            raise KernelError("attention: kept first positions or pooled blocks, not both")
+        if kparts != 1 or softcap or shared_kv or gate_per_head:
+            raise KernelError("attention: keys beyond the window go with plain keys and values only")
+        g = _gate_args(gate, gate_nsplit, gate_split_stride)
+        _check(lib, lib.mhb_attention_simt_masked(
+            _ptr(q), _ptr(cache), _ptr(out), c_int(dtype_code(q.dtype)), _ptr(part_acc), _ptr(part_ml),
+            _ptr(items), c_int(num_items), c_int(max_items), _ptr(positions), _ptr(block_table),
+            c_int(block_table.shape[-1]), _ptr(tok_part_row), c_int(nq), c_int(nkv), c_int(d), c_int(dv or d),
+            c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
+            g[0], g[1], g[2], g[3], c_int(1 if out.dtype == torch.float32 else 0),
+            c_int(1 if keep_first else 2 if pool else 0), c_int(keep_first or pool or 0),
+            c_int(1 if all_values else 0), _stream()), "attention")
+        return
     general = kparts != 1 or softcap or shared_kv or gate_per_head or out.dtype != q.dtype
     if dv is not None or sink is not None or gate is not None or general:
         g = _gate_args(gate, gate_nsplit, gate_split_stride)
@@ -1025,15 +1048,18 @@ def moe_plan_words(pairs: int, experts: int) -> int:
     return 1 + 3 * moe_max_tiles(pairs, experts) + 2 * pairs
 
 
-def moe_route(logits, correction, chosen, weights, *, outputs, top, groups=1, keep=1):
-    """Per token: softmax over the first ``outputs`` columns of the float32 Product ``logits``, choice by softmax +
-    correction inside the best ``keep`` of ``groups`` groups, ``chosen`` int32 [T, top] and the chosen outputs'
-    softmax values divided by their sum as ``weights`` float32 [T, top]."""
+def moe_route(logits, correction, chosen, weights, *, outputs, top, groups=1, keep=1, bias=None):
+    """Per token: softmax over the first ``outputs`` columns of the float32 Product ``logits`` (plus ``bias``, if
+    there is one), choice by softmax + correction (None: none) inside the best ``keep`` of ``groups`` groups,
+    ``chosen`` int32 [T, top] and the chosen outputs' softmax values divided by their sum as ``weights`` float32
+    [T, top]: without a correction that is the choice of the largest logits, weighted by the softmax over the
+    chosen logits alone."""
     lib = build.load("moe")
     T = chosen.shape[0]
-    _check(lib, lib.mhb_moe_route(*_parts_args(logits.tensor, logits.nsplit, logits.split_stride),
-                                  c_int(logits.tensor.stride(-2)), _ptr(correction), _ptr(chosen), _ptr(weights),
-                                  c_int(T), c_int(outputs), c_int(top), c_int(groups), c_int(keep), _stream()), "moe_route")
+    _check(lib, lib.mhb_moe_route_biased(*_parts_args(logits.tensor, logits.nsplit, logits.split_stride),
+                                         c_int(logits.tensor.stride(-2)), _ptr(bias), _ptr(correction), _ptr(chosen),
+                                         _ptr(weights), c_int(T), c_int(outputs), c_int(top), c_int(groups),
+                                         c_int(keep), _stream()), "moe_route")
 
 
 def moe_plan(chosen, plan, *, experts):
@@ -1083,3 +1109,88 @@ def moe_combine(y, plan, chosen, weights, h, out, *, experts, shared=None, share
                                     _ptr(weights), c_int(top), c_int(experts), _ptr(h), c_int(dtype_code(h.dtype)),
                                     c_longlong(h.stride(0)), *sh, *sg, c_int(g_ld), _ptr(out), c_int(T), c_int(W),
                                     _stream()), "moe_combine")
+
+
+# ---- keys beyond the window, mixed heads (csrc/maskparts.cu) --------------------------------------------------
+def pool_slots(page_size: int, pool: int) -> int:
+    """Pooled rows a page holds per KV head behind its keys and values: blocks of ``pool`` positions whose last
+    position lies in the page."""
+    return -(-page_size // pool)
+
+
+def pool_means(cache, positions, tok_seg, block_table, *, nkv, d, dv, page_size, pool, status=None):
+    """For every token of the step that completes a block of ``pool`` positions: the means of the block's cached
+    keys and values into the tail of the page of its last position (one layer's pool, pages of
+    nkv * page_size * (d + dv) + nkv * pool_slots * (d + dv) elements)."""
+    lib = build.load("maskparts")
+    T = positions.shape[0]
+    want = nkv * (page_size + pool_slots(page_size, pool)) * (d + dv)
+    if not cache.is_contiguous() or cache[0].numel() != want:
+        raise KernelError(f"pool_means: a page of {cache[0].numel()} elements where {want} are needed")
+    _check(lib, lib.mhb_pool_means(_ptr(cache), c_int(dtype_code(cache.dtype)), _ptr(positions), _ptr(tok_seg),
+                                   _ptr(block_table), c_int(block_table.shape[-1]), c_int(T), c_int(nkv), c_int(d),
+                                   c_int(dv), c_int(page_size), c_int(pool), c_int(cache.shape[0]), _ptr(status),
+                                   _stream()), "pool_means")
+
+
+def talk_mix(a, talk, out, *, nq, nkv, dv):
+    """out[t, h] = sum_g talk[h, g] * a[t, g, kv(h)]: ``a`` float32 [T, nq, nkv * dv] (every head's weights over the
+    values of every KV head), ``talk`` float32 [nq, nq], ``out`` [T, nq * dv]."""
+    lib = build.load("maskparts")
+    T = out.shape[0]
+    if a.dtype != torch.float32 or not a.is_contiguous() or a.numel() != T * nq * nkv * dv or not out.is_contiguous():
+        raise KernelError("talk_mix: a is contiguous float32 [T, nq, nkv * dv], out contiguous")
+    if talk.dtype != torch.float32 or tuple(talk.shape) != (nq, nq) or not talk.is_contiguous():
+        raise KernelError(f"talk_mix: the mixing matrix is contiguous float32 [{nq}, {nq}]")
+    _check(lib, lib.mhb_talk_mix(_ptr(a), _ptr(talk), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(nq),
+                                 c_int(nkv), c_int(dv), _stream()), "talk_mix")
+
+
+# ---- the gated delta rule (csrc/deltarule.cu) -------------------------------------------------------------------
+def delta_prep(proj, c0, b0, a0, taps, A_log, dt_bias, keep, tok_seg, seg_slot, positions, q, k, v, beta, decay, *,
+               heads, kv_heads, dk, dv, qscale, unit_eps):
+    """From the float32 Product ``proj`` (columns c0 .. hold [q | k | v], b0 .. the write strength's logits, a0 .. the
+    decay's): the short causal convolutions (``taps`` float32 [channels, taps]; inputs before the step from
+    ``keep`` [slots, >= (taps - 1) * channels]), silu, unit q (times ``qscale``) and k per head, beta = sigmoid,
+    decay = exp(-exp(A_log) softplus(a + dt_bias)); all outputs float32."""
+    lib = build.load("deltarule")
+    T = q.shape[0]
+    C, ntaps = taps.shape
+    if C != 2 * kv_heads * dk + heads * dv or taps.dtype != torch.float32 or not taps.is_contiguous():
+        raise KernelError("delta_prep: the filters are contiguous float32 [2 kv_heads dk + heads dv, taps]")
+    if keep.dtype != torch.float32 or keep.stride(-1) != 1 or keep.shape[-1] < (ntaps - 1) * C:
+        raise KernelError("delta_prep: a slot keeps (taps - 1) x channels float32 inputs")
+    for t in (q, k, v, beta, decay):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError("delta_prep: outputs are contiguous float32")
+    _check(lib, lib.mhb_delta_prep(*_parts_args(proj.tensor, proj.nsplit, proj.split_stride), c_int(proj.tensor.stride(-2)),
+                                   c_int(c0), c_int(b0), c_int(a0), _ptr(taps), _ptr(A_log), _ptr(dt_bias), _ptr(keep),
+                                   c_longlong(keep.stride(0)), _ptr(tok_seg), _ptr(seg_slot), _ptr(positions), _ptr(q),
+                                   _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), c_int(T), c_int(heads), c_int(kv_heads),
+                                   c_int(dk), c_int(dv), c_int(ntaps), c_float(qscale), c_float(unit_eps), _stream()),
+           "delta_prep")
+
+
+def delta_conv_keep(proj, c0, keep, tok_seg, seg_slot, positions, *, channels, taps):
+    """After delta_prep: every segment's last ``taps`` - 1 inputs (columns c0 .. of ``proj``) into its slot of ``keep``."""
+    lib = build.load("deltarule")
+    T, S = positions.shape[0], seg_slot.shape[0]
+    _check(lib, lib.mhb_delta_conv_keep(*_parts_args(proj.tensor, proj.nsplit, proj.split_stride),
+                                        c_int(proj.tensor.stride(-2)), c_int(c0), _ptr(keep), c_longlong(keep.stride(0)),
+                                        _ptr(tok_seg), _ptr(seg_slot), _ptr(positions), c_int(T), c_int(S), c_int(channels),
+                                        c_int(taps), _stream()), "delta_conv_keep")
+
+
+def delta_scan(q, k, v, beta, decay, state, out, tok_seg, seg_slot, positions, *, heads, kv_heads, dk, dv, writable=True):
+    """S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, token by token for every segment; ``state`` float32
+    [slots, >= heads * dk * dv] (a slot's rows are [heads, dk, dv]); ``out`` float32 [T, heads * dv]."""
+    lib = build.load("deltarule")
+    T, S = out.shape[0], seg_slot.shape[0]
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state.shape[-1] < heads * dk * dv:
+        raise KernelError(f"delta_scan: a slot holds float32 [{heads}, {dk}, {dv}]")
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise KernelError("delta_scan: the output is contiguous float32")
+    _check(lib, lib.mhb_delta_scan(_ptr(q), _ptr(k), _ptr(v), _ptr(beta), _ptr(decay), _ptr(state),
+                                   c_longlong(state.stride(0)), _ptr(out), _ptr(tok_seg), _ptr(seg_slot), _ptr(positions),
+                                   c_int(T), c_int(S), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv),
+                                   c_int(1 if writable else 0), _stream()), "delta_scan")

@@ -32,7 +32,7 @@ NVCC_FLAGS = [
 # Every module the package has; __graft_entry__.build() compiles all of them.
 MODULES = ("elementwise", "gemm_simt", "gemm_tc", "attention_simt", "attention_mma", "attention_tma", "attention_decode",
            "attention_tc", "sampling", "postnorm", "lightning", "attention_mma_ext", "mixparts", "gateparts", "gatedlinear",
-           "moe")
+           "moe", "maskparts", "deltarule")
 
 
 class KernelBuildError(RuntimeError):

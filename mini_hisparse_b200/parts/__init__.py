@@ -1,6 +1,6 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
-from . import (attention, block, embedding, feed_forward, gate, gated_linear, latent_attention, lightning, moe,  # noqa: F401
-               multimap_attention, norm, position, sink_attention)
+from . import (attention, block, delta_rule, embedding, feed_forward, gate, gated_linear, latent_attention,  # noqa: F401
+               lightning, moe, multimap_attention, norm, position, sink_attention, window_attention)
 from .base import (Block, CacheView, FeedForward, Mixer, Norm, Part, Product, Runtime, Segment, StepContext,
                    StepPlanner, Workspace)
 from .registry import (

@@ -48,7 +48,9 @@ class PostNormBlock(Block):
 
     Mixer and feed-forward take the un-normalised stream as input, so every kernel that writes the stream also leaves its rows
     in the compute dtype (ctx.extras["x_copy"]; the float32 path reads the stream directly).  Roles:
-    "mixer", "mixer_norm", and optionally "feed_forward" with "ff_norm", and "side".  Option: alpha.
+    "mixer", "mixer_norm", and optionally "feed_forward" with "ff_norm", and "side".  Options: alpha, and
+    ``keep`` (default 0): the stream's own share beside the norm, x <- keep x + norm(alpha x + sublayer(x)); alpha = 0
+    with keep = 1 is a block whose norms sit on the sublayers' outputs alone, x <- x + norm(sublayer(x)).
     Nothing is left pending: the block returns None.
     """
 
@@ -57,6 +59,7 @@ class PostNormBlock(Block):
     def __init__(self, spec: LayerSpec, rt):
         self.spec = spec
         self.alpha = float(spec.option("alpha", 1.0))
+        self.keep = float(spec.option("keep", 0.0))
         self.mixer = MIXERS.build(spec.part("mixer"), rt=rt)
         self.mixer_norm = NORMS.build(spec.part("mixer_norm"), rt=rt)
         self.feed_forward = self.ff_norm = self.side = None
@@ -90,10 +93,10 @@ class PostNormBlock(Block):
                 h = ctx.ws.get("x_copy", tuple(x.shape), ctx.rt.dtype)
                 K.act_rows(x, h, "copy")
         a = self.mixer.forward(h, ctx, cache)
-        h = self.mixer_norm.forward_post(x, ctx, a, alpha=self.alpha)
+        h = self.mixer_norm.forward_post(x, ctx, a, alpha=self.alpha, keep=self.keep)
         if self.feed_forward is not None:
             f = self.feed_forward.forward(h, ctx)
-            h = self.ff_norm.forward_post(x, ctx, f, alpha=self.alpha)
+            h = self.ff_norm.forward_post(x, ctx, f, alpha=self.alpha, keep=self.keep)
         if self.side is not None:
             h = self.side.forward_into(x, h, ctx)
         ctx.extras["x_copy"] = h

@@ -22,7 +22,11 @@ class RoutedExperts(FeedForward):
       ``identity`` outputs are identity experts that return h itself and store nothing.
     * ``shared_ff`` (None: none): an expert of that width that every token uses, added times sigmoid(w_sg . h).
 
-    Tensors: router, correction, e<i>.{gate, up, down}, shared.{gate, up, down, sg}.  The experts' weights are
+    * ``correction`` False: no correction tensor (the choice is by s alone, which is the choice of the largest z, and
+      the weights are the softmax over the chosen z); ``router_bias`` True: z = W_r h + b with a stored bias
+      ``router.b``.
+
+    Tensors: router, router.b, correction, e<i>.{gate, up, down}, shared.{gate, up, down, sg}.  The experts' weights are
     stacked at load ([experts, 2 ff, hidden] with gate above up, and [experts, hidden, ff]); the shared gate's row
     rides below the router's in one product.  Nothing between the router and the weighted sum goes through the host.
     """
@@ -36,6 +40,9 @@ class RoutedExperts(FeedForward):
         self.ff = int(spec["expert_ff"])
         self.shared_ff = spec.get("shared_ff")
         self.outputs = self.experts + self.identity
+        self.has_correction = bool(spec.get("correction", True))
+        self.has_bias = bool(spec.get("router_bias", False))
+        self.router_bias = None
         if self.outputs % self.groups or not 1 <= self.keep <= self.groups:
             raise ValueError(f"{self.outputs} router outputs in {self.groups} groups of which {self.keep} are kept")
         if not 1 <= self.top <= self.outputs // self.groups * self.keep:
@@ -48,8 +55,11 @@ class RoutedExperts(FeedForward):
         return ("moe", "mixparts")
 
     def parameters(self):
-        p = {"router": ParamSpec((self.outputs, self.hidden), init=("normal", 0.0, 0.3)),
-             "correction": ParamSpec((self.outputs,), role="vector", init=("normal", 0.0, 0.02))}
+        p = {"router": ParamSpec((self.outputs, self.hidden), init=("normal", 0.0, 0.3))}
+        if self.has_correction:
+            p["correction"] = ParamSpec((self.outputs,), role="vector", init=("normal", 0.0, 0.02))
+        if self.has_bias:
+            p["router.b"] = ParamSpec((self.outputs,), role="vector", init=("normal", 0.0, 0.5))
         for e in range(self.experts):
             p[f"e{e}.gate"] = ParamSpec((self.ff, self.hidden))
             p[f"e{e}.up"] = ParamSpec((self.ff, self.hidden))
@@ -63,7 +73,8 @@ class RoutedExperts(FeedForward):
     def load(self, tensors):
         rows = [tensors["router"]] + ([tensors["shared.sg"]] if self.shared_ff is not None else [])
         self.router = _pad_rows(torch.cat(rows, 0))             # [router outputs | shared gate | zeros]
-        self.correction = tensors["correction"]
+        self.correction = tensors.get("correction")
+        self.router_bias = tensors.get("router.b")
         E = self.experts
         self.gate_up = torch.stack([torch.cat((tensors[f"e{e}.gate"], tensors[f"e{e}.up"]), 0) for e in range(E)]).contiguous()
         self.down = torch.stack([tensors[f"e{e}.down"] for e in range(E)]).contiguous()
@@ -78,7 +89,7 @@ class RoutedExperts(FeedForward):
         chosen = ws.get("moe_chosen", (T, top), torch.int32)
         weights = ws.get("moe_weights", (T, top), torch.float32)
         K.moe_route(logits, self.correction, chosen, weights, outputs=self.outputs, top=top, groups=self.groups,
-                    keep=self.keep)
+                    keep=self.keep, bias=self.router_bias)
         plan = ws.get("moe_plan", (K.moe_plan_words(pairs, E),), torch.int32)
         K.moe_plan(chosen, plan, experts=E)
         act = ws.get("moe_act", (pairs, self.ff), rt.dtype)

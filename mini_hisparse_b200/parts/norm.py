@@ -16,6 +16,8 @@ class RMSNorm(Norm):
     The weight is a plain multiplier (not 1 + w) and there is no bias, as in the reference.  With
     ``offset`` (a number, usually 1) the stored tensor is a deviation around zero and the multiplier is
     offset + w: the sum is formed once at load, in float32, and the kernels see a plain weight.
+    With ``gain`` (a number) the multiplier is gain * w, formed once at load in float32: a block that adds a
+    fixed multiple of a normalised branch to the stream.
     With ``delta`` the kernel first adds it to the residual (and writes the sum back when all
     rows are processed), so the residual add costs no extra pass over memory.
     """
@@ -26,6 +28,7 @@ class RMSNorm(Norm):
         self.eps = float(spec["eps"])
         self.weight_name = spec.get("weight_name", "weight")     # "" if the tensor is named by the prefix alone
         self.offset = float(spec.get("offset", 0.0))
+        self.gain = float(spec.get("gain", 1.0))
         self.weight = None
 
     def parameters(self):
@@ -35,6 +38,8 @@ class RMSNorm(Norm):
         self.weight = tensors[self.weight_name]
         if self.offset:
             self.weight = self.weight.float() + self.offset
+        if self.gain != 1.0:
+            self.weight = self.weight.float() * self.gain
 
     def forward_post(self, x, ctx: StepContext, delta: Product | None, alpha: float = 1.0, keep: float = 0.0,
                      name="x_copy"):

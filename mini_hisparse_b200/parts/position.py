@@ -34,8 +34,10 @@ class Rotary(Position):
     computed in float32 exactly as the reference does (``theta ** (-arange(0, d, 2).float() / d)``).
 
     Parameters: head_dim, theta; optional ``rotary_dim`` (rotate only the first rotary_dim elements
-    of a head, frequencies theta ** (-(2 i) / rotary_dim)) and ``style`` ("half_split" pairs
-    (i, i + rotary_dim / 2), or "interleaved" pairs (2i, 2i + 1)).
+    of a head, frequencies theta ** (-(2 i) / rotary_dim)), ``style`` ("half_split" pairs
+    (i, i + rotary_dim / 2), or "interleaved" pairs (2i, 2i + 1)), ``scaling_factor`` (linear scaling:
+    every frequency is divided by it, so positions are read as position / factor) and ``float64_table``
+    (the frequencies are formed in float64 and rounded once to the float32 the kernels read).
     """
 
     STYLES = ("half_split", "interleaved")
@@ -52,7 +54,16 @@ class Rotary(Position):
         if self.rotary_dim % 2 or not 0 < self.rotary_dim <= self.head_dim:
             raise ValueError(f"rotary encoding needs an even rotary_dim of at most head_dim "
                              f"({self.head_dim}), got {self.rotary_dim}")
-        inv = self.theta ** (-torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim)
+        self.scaling_factor = float(spec.get("scaling_factor") or 1.0)
+        if not self.scaling_factor > 0:
+            raise ValueError("a rotary scaling factor must be positive")
+        if spec.get("float64_table"):
+            inv = (self.theta ** (-torch.arange(0, self.rotary_dim, 2, dtype=torch.float64) / self.rotary_dim)
+                   / self.scaling_factor).float()
+        else:
+            inv = self.theta ** (-torch.arange(0, self.rotary_dim, 2).float() / self.rotary_dim)
+            if self.scaling_factor != 1.0:
+                inv = inv / self.scaling_factor
         self.inv_freq = inv.to(rt.device) if rt is not None else inv
 
 

@@ -190,18 +190,25 @@ class PagedNeed(CacheNeed):
 class PagedKVNeed(PagedNeed):
     """Keys and values of every cached position: a page is [2 (K, V), kv_heads, page_size, head_dim].
     With values of another width (``v_dim``) a page is flat: the keys [kv_heads, page_size, head_dim]
-    followed by the values [kv_heads, page_size, v_dim], which for equal widths is the same memory."""
+    followed by the values [kv_heads, page_size, v_dim], which for equal widths is the same memory.
+    With ``pool`` a page has a tail: one more key and value row per KV head for every block of ``pool``
+    positions whose last position lies in the page (ceil(page_size / pool) of each), for mixers that see
+    far blocks as their means."""
 
     kv_heads: int = 1
     head_dim: int = 16
     window: int | None = None
     v_dim: int | None = None
+    pool: int | None = None
 
     def __post_init__(self):
         if self.v_dim == self.head_dim:          # one way to say it, so that equal needs compare equal
             object.__setattr__(self, "v_dim", None)
 
     def page_shape(self, page_size: int) -> tuple[int, ...]:
+        if self.pool:
+            rows = page_size + -(-page_size // self.pool)
+            return (self.kv_heads * rows * (self.head_dim + (self.v_dim or self.head_dim)),)
         if self.v_dim is None:
             return (2, self.kv_heads, page_size, self.head_dim)
         return (self.kv_heads * page_size * (self.head_dim + self.v_dim),)
