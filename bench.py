@@ -17,7 +17,7 @@ of 128 to 4,096 tokens in portions of 512 beside decoding at the Qwen2.5-14B sha
 8,192 prompt tokens plus 512 generated ones at the Qwen2.5-32B shape with the page pool sized from
 free memory; tokens a second, step-time percentiles, roofline fractions, clocks, and the layer count.
 
-    python bench.py --workload koronex|dotivik [--sizes 2k,4k]
+    python bench.py --workload koronex|dotivik|tudasun|rizovik [--sizes 2k,4k]
 
 times the Koronex or the Dotivik design beside the Qwen2 dense model at equal width, heads, feed-forward width and layer
 count (random weights): prefill of a 2,048-token prompt and decode at batch 8 with 4,096 tokens of context,
@@ -91,9 +91,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the 28 of the config")
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex", "dotivik", "tudasun"],
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + ["koronex", "dotivik", "tudasun", "rizovik"],
                     help="run a serving workload, or the two-architecture comparison, instead of the decode bench")
-    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex, dotivik or tudasun: which sizes to time")
+    ap.add_argument("--sizes", default="2k,4k", help="with --workload koronex, dotivik, tudasun or rizovik: which sizes to time")
     ap.add_argument("--graph-after", type=int, default=8,
                     help="with --workload: capture a decode graph at the N-th step that asks for it")
     args = ap.parse_args()
@@ -105,7 +105,7 @@ def main() -> int:
     if args.impl == "reference":
         return reference_arm(args)
     args.warmup = max(args.warmup, 3)
-    if args.workload in ("koronex", "dotivik", "tudasun"):
+    if args.workload in ("koronex", "dotivik", "tudasun", "rizovik"):
         if args.steps == 64:
             args.steps = 32
         return compare(args)

@@ -457,6 +457,33 @@ def tudasun_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int,
                 token_side=dict(dim=side_dim), layers=out)
 
 
+def rizovik_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int,
+                  window: int = 1024, pool: int = 64, keep_first: int = 4) -> dict:
+    """A Rizovik config.json of a real model's sizes: groups of three layers (the window with pooled blocks, the window
+    with kept first positions and mixed heads, the gated delta rule with states of head_dim x head_dim), the last two
+    layer runs using the tensors of the first layer of their kind.  Every layer has a routed
+    feed-forward: 16 experts of which a token uses 4, each ff / 4 wide, so that a token's products are as many as in a
+    gated feed-forward ``ff`` wide.  The layer that mixes heads applies every head's weights to the values of all its
+    KV heads, which its kernel takes up to 512 numbers wide: it gets at most 512 / head_dim KV heads."""
+    rot = dict(dims=head_dim // 2, base=10000.0)
+    pooled = dict(heads=heads, kv_heads=kv_heads, dim=head_dim, vdim=head_dim, scale=head_dim ** -0.5,
+                  mask=dict(size=window, pool=pool), rot=rot)
+    kept = dict(heads=heads, kv_heads=min(kv_heads, max(1, 512 // head_dim)), dim=head_dim, vdim=head_dim,
+                scale=head_dim ** -0.5, mask=dict(size=window, keep_first=keep_first),
+                rot=dict(rot, scaling=dict(factor=8.0)))
+    delta = dict(heads=heads, kv_heads=kv_heads, dim=head_dim, vdim=head_dim, conv=4)
+    moe = dict(kind="moe", expert=dict(ff=ff // 4), router=dict(experts=16, top=4))
+    kinds = [("attention", pooled), ("attention_2", kept), ("delta", delta)]
+    out = []
+    for i in range(layers):
+        kind, mixer = kinds[i % 3]
+        entry = dict(type=kind, mixer=dict(mixer), mlp=dict(moe))
+        if layers > 3 and i >= layers - 2:
+            entry["weights_of"] = i % 3                  # the first layer of its kind
+        out.append(entry)
+    return dict(architecture="Rizovik", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, layers=out)
+
+
 def qwen2_shape(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, layers: int, vocab: int) -> dict:
     return dict(architectures=["Qwen2ForCausalLM"], model_type="qwen2", vocab_size=vocab, hidden_size=width,
                 intermediate_size=ff, num_hidden_layers=layers, num_attention_heads=heads,
@@ -587,8 +614,16 @@ def architecture_point(config: dict, *, prefill_tokens=2048, batch=8, context=40
     # bytes a decode step must read: the weights once, the keys and values that every layer's window
     # still sees, and every state (read and written)
     kv = 0
+    sees = {}            # a mixer that keeps every page but reads a window (and block means, or kept first positions) only
+    for block in model.blocks:
+        mixer, need = block.mixer, block.cache_need()
+        w = getattr(mixer, "window", None)
+        if need is not None and w and getattr(need, "window", None) is None:
+            far = max(0, context - w)
+            pool, kept = getattr(mixer, "pool", 0), getattr(mixer, "keep_first", 0)
+            sees[need] = min(context, w) + (far // pool if pool else 0) + min(kept, far)
     for grp in cache.page_groups:
-        seen = context if grp.window is None else min(context, grp.window)
+        seen = sees.get(grp.need, context) if grp.window is None else min(context, grp.window)
         kv += grp.page_bytes() // page_size * seen * batch
     state = sum(2 * grp.storage[:, :batch].numel() * grp.storage.element_size() for grp in cache.state_groups)
     emb = model.embedding.weight
@@ -624,10 +659,13 @@ COMPARE_SIZES = {
 }
 
 
-DESIGN_SHAPES = {"koronex": koronex_shape, "dotivik": dotivik_shape, "tudasun": tudasun_shape, "qwen2": qwen2_shape}
+DESIGN_SHAPES = {"koronex": koronex_shape, "dotivik": dotivik_shape, "tudasun": tudasun_shape, "rizovik": rizovik_shape,
+                 "qwen2": qwen2_shape}
 # the existing model that a design is set beside: Tudasun beside Koronex, the other design with a recurrent mixer over
 # a float32 state, softmax attention with a sink, layers that read another layer's rows and a per-layer token input
-BESIDE = {"koronex": "qwen2", "dotivik": "qwen2", "tudasun": "koronex"}
+# Rizovik beside Tudasun: routed feed-forwards, a recurrent mixer over a float32 state, attention over a cache that keeps
+# every row
+BESIDE = {"koronex": "qwen2", "dotivik": "qwen2", "tudasun": "koronex", "rizovik": "tudasun"}
 
 
 def compare_architectures(sizes=("2k", "4k"), design: str = "koronex", beside: str | None = None, **kw) -> dict:

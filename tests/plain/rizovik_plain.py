@@ -82,54 +82,74 @@ def rotate_half_split(t, positions, dims, base, factor=1.0):
 
 
 # ---- pooled-window attention -------------------------------------------------------------------------
-def pooled_window_attention(h, w, p, m, eps):
-    T = h.shape[0]
-    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, pool = m["mask"]["size"], m["mask"]["pool"]
-    pos = torch.arange(T)
-    q = unit_rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]
-    k = unit_rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]
-    q = rotate_half_split(q.view(T, H, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_half_split(k.view(T, G, d), pos, m["rot"]["dims"], m["rot"]["base"])
-    v = unit_rms((h @ w[p + "v"].T).view(T, G, dv), eps)
-    nb = T // pool
-    kb = k[:nb * pool].view(nb, pool, G, d).mean(1)
-    vb = v[:nb * pool].view(nb, pool, G, dv).mean(1)
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    for i in range(T):
+def pooled_window_softmax(q, k, v, scale, size, pool, qpos=None):
+    """q [R, H, d] at the positions ``qpos`` (default 0 .. R-1), k [L, G, d], v [L, G, dv] as cached.  Query i sees the
+    positions j with 0 <= i - j < size and the mean key and value of every block of ``pool`` positions that ends at or
+    before i - size; one softmax over both.  Returns [R, H, dv]."""
+    R, H, _ = q.shape
+    G = k.shape[1]
+    qpos = list(range(R)) if qpos is None else [int(p) for p in qpos]
+    nb = k.shape[0] // pool
+    kb = k[:nb * pool].reshape(nb, pool, G, k.shape[-1]).mean(1)
+    vb = v[:nb * pool].reshape(nb, pool, G, v.shape[-1]).mean(1)
+    out = torch.zeros(R, H, v.shape[-1], dtype=q.dtype)
+    for r, i in enumerate(qpos):
         lo = max(0, i - size + 1)
         seen = max(0, (i - size + 1) // pool)          # blocks whose last position is <= i - size
         for hd in range(H):
             g = hd // (H // G)
             keys = torch.cat((kb[:seen, g], k[lo:i + 1, g]), 0)
             vals = torch.cat((vb[:seen, g], v[lo:i + 1, g]), 0)
-            a = torch.softmax(keys @ q[i, hd] * m["scale"], 0)
-            out[i, hd] = a @ vals
+            out[r, hd] = torch.softmax(keys @ q[r, hd] * scale, 0) @ vals
+    return out
+
+
+def pooled_window_attention(h, w, p, m, eps):
+    T = h.shape[0]
+    H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    pos = torch.arange(T)
+    q = (unit_rms(h @ w[p + "q"].T, eps) * w[p + "q.norm"]).view(T, H, d)
+    k = (unit_rms(h @ w[p + "k"].T, eps) * w[p + "k.norm"]).view(T, G, d)
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    if rot["dims"]:
+        q = rotate_half_split(q, pos, rot["dims"], rot["base"])
+        k = rotate_half_split(k, pos, rot["dims"], rot["base"])
+    v = unit_rms((h @ w[p + "v"].T).view(T, G, dv), eps)
+    out = pooled_window_softmax(q, k, v, m["scale"], m["mask"]["size"], m["mask"]["pool"])
     out = out.reshape(T, H * dv) * torch.sigmoid(h @ w[p + "g"].T)
     return out @ w[p + "o"].T
 
 
 # ---- attention with kept first tokens and mixed heads ------------------------------------------------
+def kept_first_mixed(q, k, v, talk, scale, size, keep, qpos=None):
+    """q [R, H, d] at ``qpos``, k [L, G, d], v [L, G, dv].  Query i sees j <= i with i - j < size or j < keep; after the
+    softmax head h's weights become sum_g talk[h, g] w_g, applied to the values of h's own KV head.  [R, H, dv]."""
+    R, H, _ = q.shape
+    L, G = k.shape[0], k.shape[1]
+    i = (torch.arange(R) if qpos is None else torch.as_tensor(qpos))[:, None]
+    j = torch.arange(L)[None, :]
+    seen = (j <= i) & ((i - j < size) | (j < keep))
+    weights = torch.zeros(H, R, L, dtype=q.dtype)
+    for hd in range(H):
+        s = q[:, hd] @ k[:, hd // (H // G)].T * scale
+        weights[hd] = torch.softmax(s.masked_fill(~seen, -math.inf), -1)
+    mixed = torch.einsum("hg,gij->hij", talk, weights)
+    return torch.stack([mixed[hd] @ v[:, hd // (H // G)] for hd in range(H)], 1)
+
+
 def kept_first_attention(h, w, p, m, eps):
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
     pos = torch.arange(T)
-    rot = m["rot"]
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
     factor = (rot.get("scaling") or {}).get("factor", 1.0)
     q = unit_rms((h @ w[p + "q"].T).view(T, H, d), eps) * w[p + "q.norm"]
     k = unit_rms((h @ w[p + "k"].T).view(T, G, d), eps) * w[p + "k.norm"]
-    q = rotate_half_split(q, pos, rot["dims"], rot["base"], factor)
-    k = rotate_half_split(k, pos, rot["dims"], rot["base"], factor)
+    if rot["dims"]:
+        q = rotate_half_split(q, pos, rot["dims"], rot["base"], factor)
+        k = rotate_half_split(k, pos, rot["dims"], rot["base"], factor)
     v = (h @ w[p + "v"].T).view(T, G, dv)
-    i, j = pos[:, None], pos[None, :]
-    seen = (j <= i) & ((i - j < size) | (j < keep))
-    weights = torch.zeros(H, T, T, dtype=h.dtype)
-    for hd in range(H):
-        s = q[:, hd] @ k[:, hd // (H // G)].T * m["scale"]
-        weights[hd] = torch.softmax(s.masked_fill(~seen, -math.inf), -1)
-    mixed = torch.einsum("hg,gij->hij", w[p + "talk"], weights)
-    out = torch.stack([mixed[hd] @ v[:, hd // (H // G)] for hd in range(H)], 1)
+    out = kept_first_mixed(q, k, v, w[p + "talk"], m["scale"], m["mask"]["size"], m["mask"].get("keep_first") or 0)
     return out.reshape(T, H * dv) @ w[p + "o"].T
 
 
@@ -141,20 +161,21 @@ def short_convolution(z, taps):
     return sum(padded[i:i + T] * taps[:, i] for i in range(K))
 
 
-def delta_rule_scan(q, k, v, beta, g):
-    """q, k [T, H, d], v [T, H, dv], beta, g [T, H]; returns o [T, H, dv]."""
+def delta_rule_scan(q, k, v, beta, g, S0=None, return_state=False):
+    """q, k [T, H, d], v [T, H, dv], beta, g [T, H]; returns o [T, H, dv] (and the last state [H, d, dv])."""
     T, H, d = q.shape
-    S = torch.zeros(H, d, v.shape[-1], dtype=q.dtype)
+    S = torch.zeros(H, d, v.shape[-1], dtype=q.dtype) if S0 is None else S0.clone()
     o = torch.zeros_like(v)
     for t in range(T):
         S = S * g[t][:, None, None]
         u = beta[t][:, None] * (v[t] - torch.einsum("hdv,hd->hv", S, k[t]))
         S = S + torch.einsum("hd,hv->hdv", k[t], u)
         o[t] = torch.einsum("hdv,hd->hv", S, q[t])
-    return o
+    return (o, S) if return_state else o
 
 
-def delta_mixer(h, w, p, m, eps):
+def delta_inputs(h, w, p, m):
+    """q, k [T, G, d] (unit vectors, q times d^-1/2), v [T, H, dv], beta and g [T, H]."""
     T = h.shape[0]
     H, G, d, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     q = silu(short_convolution(h @ w[p + "q"].T, w[p + "q.conv"])).view(T, G, d)
@@ -162,9 +183,16 @@ def delta_mixer(h, w, p, m, eps):
     v = silu(short_convolution(h @ w[p + "v"].T, w[p + "v.conv"])).view(T, H, dv)
     q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * d ** -0.5
     k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    q, k = q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1)
     beta = torch.sigmoid(h @ w[p + "b"].T)
     g = torch.exp(-torch.exp(w[p + "A_log"]) * torch.nn.functional.softplus(h @ w[p + "a"].T + w[p + "dt_bias"]))
+    return q, k, v, beta, g
+
+
+def delta_mixer(h, w, p, m, eps):
+    T = h.shape[0]
+    H, G, dv = m["heads"], m["kv_heads"], m["vdim"]
+    q, k, v, beta, g = delta_inputs(h, w, p, m)
+    q, k = q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1)
     o = delta_rule_scan(q, k, v, beta, g)
     o = unit_rms(o, eps) * w[p + "norm"]
     return (o.reshape(T, H * dv) * silu(h @ w[p + "g"].T)) @ w[p + "o"].T

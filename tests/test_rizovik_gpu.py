@@ -1,0 +1,723 @@
+"""Rizovik through the engine against the plain implementation of tests/plain/rizovik_plain.py.
+
+Small configurations made here (none is anyone's model), random weights from a seed.  Covered: the kernels of each
+mechanism alone (norms per head and over whole projections with the value norm and a page's tail left alone; block
+means at page borders for blocks that divide a page and blocks that do not; the window with pooled blocks and the
+window with kept first positions and mixed heads, with one key made to stand out far back, just inside and just
+outside the window, in the block that is just seen and in the one that is not yet, among the kept positions and
+right behind them, for prompt portions, short portions and decoded tokens, with and without key splits; the short
+convolutions over a step's edge with the kept inputs; the delta rule from a slot's state and from zero; the router
+by logits with a bias); whole prompts; prefill against token-by-token decoding through captured graphs; portions
+down to two tokens; mixed batches over a tight pool whose freed pages are poisoned; slots used again; long decoding;
+sizes that are equal or 1; layers that run another layer's tensors; generation through Engine and its scheduler;
+the command line; bin/trace_run.
+"""
+import copy
+import json
+
+import pytest
+import torch
+
+import schedules as S
+from conftest import TraceRun, random_tokens, row_rms_error
+from plain import rizovik_plain as P
+from test_dotivik_gpu import Parts, dev_i, run_steps
+
+pytestmark = pytest.mark.gpu
+
+
+def pooled(heads, kv_heads, dim, vdim, size, pool, rot=None, base=3000.0, scale=0.3):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, mask=dict(size=size, pool=pool))
+    if rot is not None:
+        m["rot"] = dict(dims=rot, base=base)
+    return m
+
+
+def kept(heads, kv_heads, dim, vdim, size, keep, rot=None, base=3000.0, factor=None, scale=0.3):
+    m = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=scale, mask=dict(size=size, keep_first=keep))
+    if rot is not None:
+        m["rot"] = dict(dims=rot, base=base)
+        if factor is not None:
+            m["rot"]["scaling"] = dict(factor=factor)
+    return m
+
+
+def delta(heads, kv_heads, dim, vdim, conv):
+    return dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, conv=conv)
+
+
+def moe(experts, top, ff):
+    return dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+
+
+def layer(kind, mixer, mlp=None, weights_of=None):
+    out = dict(type=kind, mixer=mixer, mlp=mlp)
+    if weights_of is not None:
+        out["weights_of"] = weights_of
+    return out
+
+
+def model(vocab, width, layers, mult=0.5, eps=1e-5):
+    return dict(architecture="Rizovik", vocab=vocab, width=width, norm=dict(eps=eps), residual_mult=mult, layers=layers)
+
+
+# A: every branch at once, with windows short enough that prompts of a hundred tokens pass them many times: blocks
+# that divide a page and keys narrower than values, kept positions under scaled frequencies, a delta layer without a
+# feed-forward, and three layers that run an earlier layer's tensors over caches and states of their own.
+_A0, _A1, _A2 = pooled(4, 2, 24, 40, 20, 4, rot=8, base=5000.0), kept(6, 3, 16, 24, 24, 3, rot=16, base=1000.0, factor=4.0), \
+    delta(4, 2, 16, 24, 3)
+CFG_A = model(199, 96, [
+    layer("attention", _A0, moe(6, 2, 32)), layer("attention_2", _A1, moe(5, 3, 24)), layer("delta", _A2),
+    layer("attention", _A0, moe(6, 2, 32), weights_of=0), layer("delta", _A2, weights_of=2),
+    layer("attention_2", _A1, moe(5, 3, 24), weights_of=1),
+    layer("delta", delta(2, 2, 24, 16, 4), moe(4, 1, 48))], mult=0.7)
+# B: values that a usual model makes different are equal or 1 here: one head, as many KV heads as heads, blocks of one
+# position and blocks of five that straddle the pages of eight, a window of one position, no kept position and one,
+# no rotation and a rotation of the whole head, unscaled frequencies, filters of one and two taps, one expert a token
+# and a single expert, a multiplier of 1, a width that no tensor-core product takes.
+CFG_B = model(97, 100, [
+    layer("attention", pooled(1, 1, 20, 20, 7, 1), moe(3, 1, 20)),
+    layer("attention_2", kept(1, 1, 12, 20, 5, 0, rot=12, base=100.0), moe(1, 1, 12)),
+    layer("delta", delta(1, 1, 12, 12, 1)),
+    layer("attention", pooled(3, 3, 12, 8, 1, 5, rot=12, base=50.0), moe(4, 4, 16)),
+    layer("attention_2", kept(2, 2, 20, 12, 9, 1), moe(2, 1, 8)),
+    layer("delta", delta(5, 1, 4, 20, 2), moe(3, 2, 28))], mult=1.0)
+# C: sizes of a real model's order: heads of 128 and 64, a state of 128 x 128, windows of some hundred positions,
+# blocks of 16 under pages of 32.
+CFG_C = model(300, 256, [
+    layer("attention", pooled(8, 2, 64, 64, 96, 16, rot=32, base=1e6, scale=0.12), moe(8, 2, 128)),
+    layer("delta", delta(4, 2, 128, 128, 4), moe(16, 4, 64)),
+    layer("attention_2", kept(4, 2, 128, 128, 64, 4, rot=64, base=1e6, factor=8.0, scale=0.09), moe(8, 2, 128)),
+    layer("delta", delta(4, 2, 128, 128, 4), moe(16, 4, 64), weights_of=1)], mult=0.5)
+CONFIGS = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+PAGES = {"A": 16, "B": 8, "C": 32}
+# A row's error: the root mean square of (got - plain) as a share of the row's root mean square.  float32: the plain
+# model is computed in float64; the design computed in float32 in any order differs from that by some 1e-6 on average
+# and by more at single positions (a sublayer's result that nearly cancels is normalised right after).  bfloat16: the
+# router sees the bfloat16 rounding of its input, so that at some tokens another expert wins a close call than in
+# the plain model.  These models have a router in nearly every layer over a handful of experts, and every sublayer's
+# result is normalised before it is added, so such a token's row differs as a whole, and through the caches and states
+# a little of that reaches every later token of its request (a handful of tokens out of the five hundred of a run):
+# the mean over all rows and the worst row are held loosely against the plain model, every schedule is compared with
+# the WHOLE prompt in the same dtype as well, and the float32 runs hold the same code to 1.5e-4.
+BF16_MEAN, BF16_WORST = 0.12, 1.6
+F32_MEAN, F32_ROW = 1.5e-5, 1.5e-4
+BF16_CUT = 0.5
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    from mini_hisparse_b200 import write_random_model
+
+    out = {}
+    for name, cfg in CONFIGS.items():
+        folder = tmp_path_factory.mktemp(f"rizovik{name}")
+        write_random_model(cfg, 41, folder, dtype=torch.bfloat16, matrix_std=0.15)
+        out[name] = (folder, *P.load_folder(folder))
+    return out
+
+
+def requests_for(cfg, lengths, seed=0):
+    return {f"r{i}": random_tokens(cfg["vocab"], n, seed + i) for i, n in enumerate(lengths)}
+
+
+def row_errors(got, ref):
+    return (got.double() - ref.double()).pow(2).mean(-1).sqrt() / ref.double().pow(2).mean(-1).sqrt()
+
+
+def check_against_plain(got, refs, dtype):
+    for rid, ref in refs.items():
+        assert got[rid].shape == ref.shape
+    err = torch.cat([row_errors(got[rid], ref) for rid, ref in refs.items()])
+    mean, worst = (F32_MEAN, F32_ROW) if dtype == "float32" else (BF16_MEAN, BF16_WORST)
+    assert float(err.mean()) < mean and float(err.max()) < worst, \
+        f"mean row error {float(err.mean()):.3g}, worst {float(err.max()):.3g} at {int(err.argmax())} of all rows"
+
+
+def close(got, ref, tol, what=""):
+    scale = float(ref.abs().max())
+    err = float((got.double().cpu() - ref.double()).abs().max())
+    assert err < tol * scale, f"{what}: {err:.3g} beside values up to {scale:.3g}"
+
+
+# ---- a paged pool filled by hand ----------------------------------------------------------------------------
+class Pool:
+    """One layer's pages with a tail for block means, one request's block table over shuffled pages."""
+
+    def __init__(self, L, G, d, dv, P_, pool, dtype, seed=0):
+        from mini_hisparse_b200.kernels import api as K
+
+        self.G, self.d, self.dv, self.P, self.pool = G, d, dv, P_, pool
+        self.slots = K.pool_slots(P_, pool) if pool else 0
+        self.page_elems = G * (P_ + self.slots) * (d + dv)
+        n_pages = -(-L // P_)
+        g = torch.Generator().manual_seed(seed)
+        self.table = torch.randperm(n_pages + 3, generator=g)[:n_pages].to(torch.int32)
+        self.storage = torch.full((n_pages + 3, self.page_elems), 1e30 if dtype == torch.float32 else 1e30,
+                                  dtype=dtype, device="cuda")
+
+    def fill(self, k, v):
+        """k [L, G, d], v [L, G, dv] into their pages (rounded to the pool's dtype); returns what the cache holds."""
+        L = k.shape[0]
+        st = self.storage.cpu()
+        for p in range(L):
+            page, w = int(self.table[p // self.P]), p % self.P
+            kp = st[page, : self.G * self.P * self.d].view(self.G, self.P, self.d)
+            vp = st[page, self.G * self.P * self.d: self.G * self.P * (self.d + self.dv)].view(self.G, self.P, self.dv)
+            kp[:, w], vp[:, w] = k[p].to(st.dtype), v[p].to(st.dtype)
+        self.storage.copy_(st)
+        return k.to(st.dtype).double(), v.to(st.dtype).double()
+
+    def means(self):
+        """(keys [blocks, G, d], values [blocks, G, dv]) as the pages' tails hold them, NaN where nothing was written."""
+        st = self.storage.cpu().double()
+        kv = self.G * self.P * (self.d + self.dv)
+        out = {}
+        for i, page in enumerate(self.table.tolist()):
+            kt = st[page, kv: kv + self.G * self.slots * self.d].view(self.G, self.slots, self.d)
+            vt = st[page, kv + self.G * self.slots * self.d:].view(self.G, self.slots, self.dv)
+            first = (i * self.P) // self.pool
+            for s in range(self.slots):
+                b = first + s
+                if i * self.P <= b * self.pool + self.pool - 1 < (i + 1) * self.P:
+                    out[b] = (kt[:, s], vt[:, s])
+        return out
+
+
+def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_dtype, split_sms=148, **opts):
+    """Plan the step's attention for one request's segments and run the CUDA-core kernel and the merge."""
+    from mini_hisparse_b200.kernels import api as K
+    from mini_hisparse_b200.parts.attention import AttentionShape, plan_attention
+
+    T = sum(s.count for s in segments)
+    plan = plan_attention(AttentionShape(nq, pool_.G, window, 16), segments, T, sm_count=split_sms)
+    n = plan.n_small + plan.n_big
+    part_acc = torch.empty(max(1, plan.part_rows), nq, out_width, device="cuda")
+    part_ml = torch.empty(max(1, plan.part_rows), nq, 2, device="cuda")
+    o = torch.zeros(T, nq, out_width, dtype=out_dtype, device="cuda")
+    tables = dev_i(pool_.table[None, :].repeat(len(segments), 1))
+    positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
+    tpr, tns = dev_i(torch.from_numpy(plan.tok_part_row)), dev_i(torch.from_numpy(plan.tok_nsplit))
+    K.attention_simt(q_rows, pool_.storage, o, part_acc, part_ml, dev_i(torch.from_numpy(plan.items)), n, n, positions,
+                     tables, tpr, nq=nq, nkv=pool_.G, d=pool_.d, dv=pool_.dv, page_size=pool_.P, window=window,
+                     scale=scale, **opts)
+    if plan.part_rows:
+        gate = {k: opts[k] for k in ("gate", "gate_nsplit", "gate_split_stride") if k in opts}
+        K.attention_combine(part_acc, part_ml, tpr, tns, o, nq=nq, d=out_width, **gate)
+    return o.float().cpu().double(), plan
+
+
+def segments_of(spans):
+    from mini_hisparse_b200.parts.base import Segment
+
+    out, off = [], 0
+    for i, (start, count) in enumerate(spans):
+        out.append(Segment(i, 0, start, count, off))
+        off += count
+    return out
+
+
+# ---- the mechanisms alone ---------------------------------------------------------------------------------
+@pytest.mark.parametrize("nq,nkv,dk,dv,rdim,per_head,v_norm,pool,P_", [
+    (4, 2, 24, 40, 8, False, True, 4, 16), (6, 3, 16, 24, 16, True, False, 0, 16), (1, 1, 20, 20, 0, False, True, 5, 8),
+    (2, 2, 128, 64, 64, True, True, 3, 32), (3, 1, 12, 8, 12, True, False, 0, 7)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norms_rotation_and_append(nq, nkv, dk, dv, rdim, per_head, v_norm, pool, P_, dtype):
+    """q and k normalised over the whole projection or head by head (one weight for all heads), the first rdim elements
+    of a head rotated, every head's value by its own root mean square, over split products; rows land in their pages
+    and a page's tail is left alone."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(nq * dk + dv)
+    T, nsplit, eps = 21, 2, 1e-5
+    qw, kw, vw = nq * dk, nkv * dk, nkv * dv
+    ld = qw + kw + vw + 5
+    proj = torch.randn(nsplit, T, ld, generator=g) * 2
+    z = proj.double().sum(0)
+    wq = 1 + 0.2 * torch.randn(dk if per_head else qw, generator=g)
+    wk = 1 + 0.2 * torch.randn(dk if per_head else kw, generator=g)
+    pos = torch.arange(30, 30 + T)
+    if per_head:
+        q = P.unit_rms(z[:, :qw].view(T, nq, dk), eps) * wq.double()
+        k = P.unit_rms(z[:, qw:qw + kw].view(T, nkv, dk), eps) * wk.double()
+    else:
+        q = (P.unit_rms(z[:, :qw], eps) * wq.double()).view(T, nq, dk)
+        k = (P.unit_rms(z[:, qw:qw + kw], eps) * wk.double()).view(T, nkv, dk)
+    inv = None
+    if rdim:
+        q, k = P.rotate_half_split(q, pos, rdim, 700.0, 2.0), P.rotate_half_split(k, pos, rdim, 700.0, 2.0)
+        inv = (700.0 ** (-torch.arange(0, rdim, 2, dtype=torch.float64) / rdim) / 2.0).float().cuda()
+    v = z[:, qw + kw:qw + kw + vw].view(T, nkv, dv)
+    if v_norm:
+        v = P.unit_rms(v, eps)
+    pl = Pool(30 + T, nkv, dk, dv, P_, pool, dtype)
+    before = pl.storage.clone()
+    q_out = torch.empty(T, qw, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pd = proj.cuda()
+    K.qknorm_rope_append(pd, wq.cuda(), wk.cuda(), eps, dev_i(pos), dev_i([0] * T), dev_i(pl.table[None]), inv, rdim, q_out,
+                         pl.storage, nq=nq, nkv=nkv, dk=dk, dv=dv, page_size=P_, nsplit=nsplit, split_stride=pd.stride(0),
+                         status=status, per_head=per_head, v_eps=eps if v_norm else 0.0,
+                         page_extra=nkv * pl.slots * (dk + dv))
+    assert int(status) == 0
+    tol = 3e-6 if dtype == torch.float32 else 0.005
+    close(q_out.float().view(T, nq, dk), q, tol, "q")
+    st = pl.storage.cpu().double()
+    for t in range(T):
+        page, w = int(pl.table[(30 + t) // P_]), (30 + t) % P_
+        kp = st[page, : nkv * P_ * dk].view(nkv, P_, dk)[:, w]
+        vp = st[page, nkv * P_ * dk: nkv * P_ * (dk + dv)].view(nkv, P_, dv)[:, w]
+        close(kp, k[t], tol, "cached key")
+        close(vp, v[t], tol, "cached value")
+    if pl.slots:
+        assert torch.equal(pl.storage[:, nkv * P_ * (dk + dv):], before[:, nkv * P_ * (dk + dv):])
+
+
+@pytest.mark.parametrize("G,d,dv,P_,pool", [(2, 24, 40, 16, 4), (1, 20, 20, 8, 5), (3, 12, 8, 8, 1), (2, 64, 64, 32, 16),
+                                            (1, 16, 8, 7, 3), (2, 8, 8, 4, 9)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_means_land_in_the_page_of_their_last_position(G, d, dv, P_, pool, dtype):
+    """Blocks that divide a page, blocks that straddle pages and blocks longer than a page, written over two steps (the
+    second starts in the middle of a block); an unfinished block writes nothing."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(d + P_)
+    L = 5 * max(P_, pool) + pool // 2 + 1
+    k, v = torch.randn(L, G, d, generator=g), torch.randn(L, G, dv, generator=g)
+    pl = Pool(L, G, d, dv, P_, pool, dtype)
+    kc, vc = pl.fill(k, v)
+    cut = 2 * pool + pool // 2 + 1
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for lo, hi in ((0, cut), (cut, L)):
+        K.pool_means(pl.storage, dev_i(torch.arange(lo, hi)), dev_i([0] * (hi - lo)), dev_i(pl.table[None]), nkv=G, d=d,
+                     dv=dv, page_size=P_, pool=pool, status=status)
+    assert int(status) == 0
+    got = pl.means()
+    tol = 2e-6 if dtype == torch.float32 else 0.005
+    assert L // pool >= 5
+    for b in range(L // pool):
+        close(got[b][0], kc[b * pool:(b + 1) * pool].mean(0), tol, f"mean key of block {b}")
+        close(got[b][1], vc[b * pool:(b + 1) * pool].mean(0), tol, f"mean value of block {b}")
+    for b, (kt, vt) in got.items():
+        if b >= L // pool:
+            assert float(kt.abs().min()) > 1e29          # untouched
+
+
+def standing_out(k, q_row, at, strength=14.0):
+    """Make the key at ``at`` the one the query row looks at: it points along the query."""
+    k[at] = q_row / q_row.norm() * strength
+
+
+@pytest.mark.parametrize("H,G,d,dv,P_,size,pool,L", [(4, 2, 24, 40, 16, 20, 4, 150), (1, 1, 20, 20, 8, 7, 5, 90),
+                                                     (3, 3, 12, 8, 8, 1, 1, 40), (8, 2, 64, 64, 32, 96, 16, 700),
+                                                     (2, 1, 16, 24, 7, 10, 3, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_with_pooled_blocks(H, G, d, dv, P_, size, pool, L, dtype):
+    """The last query of a prompt portion, of a portion of three and a decoded token each get one key that stands
+    out: the oldest position inside the window, the position right before it (seen only once its block is pooled), a
+    position of the newest pooled block, one of the block that is not pooled yet, and one far back.  The kernel's
+    output follows the plain function in every case, with a gate on the output, key splits or none."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(H * d + L)
+    scale = 0.25
+    spans = [(L - 41, 30), (L - 11, 3), (L - 8, 1), (L - 7, 2), (L - 5, 1), (L - 4, 4)]
+    segs = segments_of(spans)
+    T = sum(c for _, c in spans)
+    qpos = torch.cat([torch.arange(s, s + c) for s, c in spans])
+    gate = torch.randn(T, H * dv + 3, generator=g)
+    for case in ("window_in", "window_out", "pool_in", "pool_out", "far", "first"):
+        q = torch.randn(T, H, d, generator=g)
+        k, v = torch.randn(L, G, d, generator=g), torch.randn(L, G, dv, generator=g)
+        for row in (29, 32, 33, T - 1):                    # ends of the portions, the decoded token, the last row
+            i = int(qpos[row])
+            seen = max(0, (i - size + 1) // pool)
+            at = {"window_in": max(0, i - size + 1), "window_out": max(0, i - size), "far": min(3, L - 1), "first": 0,
+                  "pool_in": max(0, seen * pool - 1), "pool_out": min(i, seen * pool)}[case]
+            for hd in range(H):
+                if hd % (H // G) == 0:
+                    k[at, hd // (H // G)] = q[row, hd] / q[row, hd].norm() * (14.0 / scale / float(q[row, hd].norm()))
+        pl = Pool(L, G, d, dv, P_, pool, dtype, seed=3)
+        kc, vc = pl.fill(k, v)
+        K.pool_means(pl.storage, dev_i(torch.arange(L)), dev_i([0] * L), dev_i(pl.table[None]), nkv=G, d=d, dv=dv,
+                     page_size=P_, pool=pool)
+        qd = q.to(dtype).cuda()
+        ref = P.pooled_window_softmax(qd.cpu().double(), kc, vc, scale, size, pool, qpos=qpos)
+        ref = ref * torch.sigmoid(gate[:, 2:2 + H * dv].double()).view(T, H, dv)
+        for sms in (148, 100000):                          # as planned for this GPU, and with every short segment split
+            got, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=dv,
+                                      out_dtype=dtype, split_sms=sms, pool=pool, gate=gate.cuda()[:, 2:2 + H * dv])
+            close(got, ref, 3e-6 if dtype == torch.float32 else 0.012, f"{case}, {plan.part_rows} partial rows")
+        if case == "window_out" and pool > 1:     # the plain function itself tells a window one position wider apart
+            other = P.pooled_window_softmax(qd.cpu().double(), kc, vc, scale, size + 1, pool, qpos=qpos)
+            assert float((other * torch.sigmoid(gate[:, 2:2 + H * dv].double()).view(T, H, dv) - ref).abs().max()) > 0.05
+
+
+@pytest.mark.parametrize("H,G,d,dv,P_,size,keep,L", [(6, 3, 16, 24, 16, 24, 3, 150), (1, 1, 12, 20, 8, 5, 0, 60),
+                                                     (2, 2, 20, 12, 8, 9, 1, 70), (4, 2, 128, 128, 32, 64, 4, 600),
+                                                     (4, 1, 32, 16, 7, 6, 9, 50)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_window_with_kept_first_positions_and_mixed_heads(H, G, d, dv, P_, size, keep, L, dtype):
+    """One key stands out for the last rows of a portion, of a short portion and of decoded tokens: the last kept
+    position, the first one that is not kept, the window's oldest position and the one before it.  Every head's
+    weights go over the values of all KV heads; the mix of the heads follows."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(H * d + L)
+    scale = 0.25
+    spans = [(L - 41, 30), (L - 11, 3), (L - 8, 1), (L - 7, 2), (L - 5, 1), (L - 4, 4)]
+    segs = segments_of(spans)
+    T = sum(c for _, c in spans)
+    qpos = torch.cat([torch.arange(s, s + c) for s, c in spans])
+    talk = torch.randn(H, H, generator=g)
+    for case in ("first_in", "first_out", "window_in", "window_out"):
+        q = torch.randn(T, H, d, generator=g)
+        k, v = torch.randn(L, G, d, generator=g), torch.randn(L, G, dv, generator=g)
+        for row in (29, 32, 33, T - 1):
+            i = int(qpos[row])
+            at = {"first_in": max(0, keep - 1), "first_out": keep, "window_in": i - size + 1, "window_out": i - size}[case]
+            for hd in range(H):
+                if hd % (H // G) == 0:
+                    k[at, hd // (H // G)] = q[row, hd] / q[row, hd].norm() * (14.0 / scale / float(q[row, hd].norm()))
+        pl = Pool(L, G, d, dv, P_, 0, dtype, seed=5)
+        kc, vc = pl.fill(k, v)
+        qd = q.to(dtype).cuda()
+        ref = P.kept_first_mixed(qd.cpu().double(), kc, vc, talk.double(), scale, size, keep, qpos=qpos)
+        for sms in (148, 100000):
+            wide, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=G * dv,
+                                       out_dtype=torch.float32, split_sms=sms, keep_first=keep, all_values=True)
+            out = torch.empty(T, H * dv, dtype=dtype, device="cuda")
+            K.talk_mix(wide.float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv)
+            close(out.float().view(T, H, dv), ref, 3e-6 if dtype == torch.float32 else 0.012, case)
+        if case in ("first_out", "window_out") and keep + size + 2 < L - 41:
+            other = P.kept_first_mixed(qd.cpu().double(), kc, vc, talk.double(), scale, size + (case == "window_out"),
+                                       keep + (case == "first_out"), qpos=qpos)
+            assert float((other - ref).abs().max()) > 0.05
+
+
+@pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 16, 24, 3), (1, 1, 12, 12, 1), (5, 1, 4, 20, 2), (4, 2, 128, 128, 4),
+                                             (2, 2, 24, 16, 4), (3, 3, 40, 72, 5), (2, 1, 200, 8, 2)])
+def test_delta_rule_inputs_and_recurrence(H, G, dk, dv, taps):
+    """Four segments in one step: a long one from position 0 in a slot that holds another request's state and kept
+    inputs (neither may be seen), one that goes on from its slot (its first taps - 1 rows reach back into the kept
+    inputs), a single token, a portion of two.  The inputs, the outputs, the new states and the new kept inputs follow
+    the plain functions; a reader that may not write leaves its slots alone."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(dk * dv + taps)
+    counts, starts, slots = [70, 37, 1, 2], [0, 9, 40, 5], [2, 0, 1, 3]
+    T, nsplit = sum(counts), 2
+    QK, VW = G * dk, H * dv
+    C = 2 * QK + VW
+    ld = C + 2 * H + VW + 3
+    proj = torch.randn(nsplit, T, ld, generator=g)
+    z = proj.double().sum(0)
+    filt = torch.randn(C, taps, generator=g) * 0.6
+    A_log, dt_bias = torch.randn(H, generator=g) * 0.5 - 1, torch.randn(H, generator=g)
+    state_elems = H * dk * dv
+    slots0 = torch.randn(4, state_elems + (taps - 1) * C, generator=g)
+    tok_seg = sum(([i] * n for i, n in enumerate(counts)), [])
+    pos = sum((list(range(s, s + n)) for s, n in zip(starts, counts)), [])
+    w = {"q.conv": filt[:QK].double(), "k.conv": filt[QK:2 * QK].double(), "v.conv": filt[2 * QK:].double()}
+    refs = dict(q=[], k=[], v=[], beta=[], g=[], o=[])
+    ref_slots = slots0.double().clone()
+    off = 0
+    for n, st, sl in zip(counts, starts, slots):
+        rows = z[off:off + n]
+        kept_rows = slots0[sl, state_elems:].double().view(max(taps - 1, 0), C) if taps > 1 else torch.zeros(0, C, dtype=torch.float64)
+        before = torch.zeros_like(kept_rows) if st == 0 else kept_rows
+        x = torch.cat((before, rows[:, :C]), 0)             # inputs from taps - 1 positions before the segment
+        y = sum(x[i:i + n] * filt.double()[:, i] for i in range(taps))
+        y = P.silu(y)
+        q, k, v = y[:, :QK].view(n, G, dk), y[:, QK:2 * QK].view(n, G, dk), y[:, 2 * QK:].view(n, H, dv)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        beta = torch.sigmoid(rows[:, C:C + H])
+        gg = torch.exp(-torch.exp(A_log.double()) * torch.nn.functional.softplus(rows[:, C + H:C + 2 * H] + dt_bias.double()))
+        S0 = torch.zeros(H, dk, dv, dtype=torch.float64) if st == 0 else slots0[sl, :state_elems].double().view(H, dk, dv)
+        o, Sn = P.delta_rule_scan(q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1), v, beta, gg, S0, True)
+        ref_slots[sl, :state_elems] = Sn.reshape(-1)
+        if taps > 1:
+            ref_slots[sl, state_elems:] = x[-(taps - 1):].reshape(-1)
+        for name, val in zip(("q", "k", "v", "beta", "g", "o"), (q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1), beta, gg, o.reshape(n, -1))):
+            refs[name].append(val)
+        off += n
+    refs = {n_: torch.cat(v_) for n_, v_ in refs.items()}
+    # the plain model's own convolution gives the same rows for the segment that starts at 0
+    if taps > 1:
+        mine = P.silu(P.short_convolution(z[:70, 2 * QK:C], w["v.conv"]))
+        assert float((mine - refs["v"][:70]).abs().max()) < 1e-9
+
+    def run(writable):
+        sl = slots0.cuda().clone()
+        pd = proj.cuda()
+        prod = Parts(pd, nsplit)
+        q, k = torch.empty(T, QK, device="cuda"), torch.empty(T, QK, device="cuda")
+        v, beta, dec = torch.empty(T, VW, device="cuda"), torch.empty(T, H, device="cuda"), torch.empty(T, H, device="cuda")
+        ctx = (dev_i(tok_seg), dev_i(slots), dev_i(pos))
+        keep = sl[:, state_elems:]
+        K.delta_prep(prod, 0, C, C + H, filt.cuda(), A_log.cuda(), dt_bias.cuda(), keep, *ctx, q, k, v, beta, dec, heads=H,
+                     kv_heads=G, dk=dk, dv=dv, qscale=dk ** -0.5, unit_eps=1e-6)
+        if writable and taps > 1:
+            K.delta_conv_keep(prod, 0, keep, *ctx, channels=C, taps=taps)
+        o = torch.zeros(T, VW, device="cuda")
+        K.delta_scan(q, k, v, beta, dec, sl, o, *ctx, heads=H, kv_heads=G, dk=dk, dv=dv, writable=writable)
+        return dict(q=q, k=k, v=v, beta=beta, g=dec, o=o), sl
+
+    got, sl = run(True)
+    for name in ("q", "k", "v", "beta", "g"):
+        close(got[name], refs[name], 3e-6, name)
+    off = 0
+    for n in counts:                   # every segment against its own scale
+        close(got["o"][off:off + n], refs["o"][off:off + n], 2e-5, "outputs")
+        off += n
+    close(sl[:, :state_elems], ref_slots[:, :state_elems], 1e-5, "states")
+    if taps > 1:
+        close(sl[:, state_elems:], ref_slots[:, state_elems:], 1e-6, "kept inputs")
+    got2, sl2 = run(False)
+    assert torch.equal(sl2.cpu(), slots0)
+    close(got2["o"], refs["o"], 2e-5, "read-only outputs")
+
+
+def test_the_delta_rule_remembers_and_overwrites():
+    """A key written once with beta = 1 and no decay is read back exactly hundreds of tokens later, and writing the same
+    key again REPLACES its value (the rule's correction), where a plain outer-product sum would add to it."""
+    from mini_hisparse_b200.kernels import api as K
+
+    H, dk, dv, T = 1, 16, 8, 300
+    g = torch.Generator().manual_seed(1)
+    k = torch.nn.functional.normalize(torch.randn(T, dk, generator=g), dim=-1) * 0.05
+    key = torch.zeros(dk)
+    key[3] = 1.0
+    k[:, 3] = 0.0                      # everything else is orthogonal to the special key
+    k[0], k[150] = key, key
+    v = torch.randn(T, dv, generator=g)
+    q = torch.zeros(T, dk)
+    q[149], q[299] = key, key
+    beta, dec = torch.ones(T, 1), torch.ones(T, 1)
+    o = torch.zeros(T, dv, device="cuda")
+    state = torch.zeros(1, dk * dv, device="cuda")
+    K.delta_scan(q.cuda(), k.cuda(), v.cuda(), beta.cuda(), dec.cuda(), state, o, dev_i([0] * T), dev_i([0]),
+                 dev_i(torch.arange(T)), heads=H, kv_heads=1, dk=dk, dv=dv)
+    ref = P.delta_rule_scan(q.double().view(T, 1, dk), k.double().view(T, 1, dk), v.double().view(T, 1, dv), beta.double(),
+                            dec.double()).view(T, dv)
+    close(o, ref, 1e-5, "outputs")
+    close(o[149], v[0].double(), 1e-5, "the first write, read back")
+    close(o[299], v[150].double(), 1e-5, "the second write replaced the first")
+
+
+@pytest.mark.parametrize("T,n,top,nsplit", [(40, 6, 2, 1), (9, 1, 1, 2), (33, 16, 4, 2), (5, 4, 4, 1), (70, 40, 3, 1)])
+def test_router_by_logits_with_a_bias(T, n, top, nsplit):
+    """The largest logits (after the bias) win; their weights are the softmax over the chosen logits alone."""
+    from mini_hisparse_b200.kernels import api as K
+
+    g = torch.Generator().manual_seed(T + n)
+    z = torch.randn(nsplit, T, n + 3, generator=g) * 2
+    bias = torch.randn(n, generator=g) * 3          # large enough to change who wins
+    zd = z.cuda()
+    chosen = torch.empty(T, top, dtype=torch.int32, device="cuda")
+    weights = torch.empty(T, top, device="cuda")
+    K.moe_route(Parts(zd if nsplit > 1 else zd[0], nsplit), None, chosen, weights, outputs=n, top=top, bias=bias.cuda())
+    logits = z.double().sum(0)[:, :n] + bias.double()
+    ref_top, ref_idx = torch.topk(logits, top, -1)
+    assert torch.equal(chosen.cpu().long(), ref_idx)
+    close(weights, torch.softmax(ref_top, -1), 3e-6, "weights")
+    if n > top:
+        assert not torch.equal(torch.topk(z.double().sum(0)[:, :n], top, -1)[1], ref_idx)       # the bias matters
+
+
+# ---- the model through the step function ---------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_every_schedule_agrees_with_the_plain_model(models, name, dtype):
+    """Whole prompts; most of a prompt and then its tail token by token, three requests side by side (captured
+    graphs; the windows pass over decoded tokens); portions of changing size down to two tokens; mixed batches with
+    up to four live requests over a pool that holds no more than they need, so that pages and slots are used again
+    (freed pages are poisoned).  Every position is compared."""
+    folder, cfg, w = models[name]
+    reqs = requests_for(cfg, [150, 1, 23, 97, 64, 2, 131])
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    whole = None
+    for steps in (S.whole(reqs), S.tail_one_by_one(reqs, tail=45), S.changing_portions(reqs), S.mixed(reqs, seed=3)):
+        got, runner, cache = run_steps(folder, dtype, steps, page_size=PAGES[name])
+        check_against_plain(got, refs, dtype)
+        whole = whole or got
+        worst = max(row_rms_error(got[rid], whole[rid]) for rid in reqs)
+        assert worst < (F32_ROW if dtype == "float32" else BF16_CUT)
+    assert all(g["pages_reused"] > 0 for g in cache["page_groups"])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_stream_after_every_layer(models, dtype):
+    """The residual stream after every run entry (a layer that runs another's tensors counts on its own)."""
+    from mini_hisparse_b200 import CacheConfig, CacheManager, load_model
+    from mini_hisparse_b200.engine import ModelRunner, StepEntry
+
+    folder, cfg, w = models["A"]
+    toks = random_tokens(cfg["vocab"], 75, 12)
+    _, streams = P.forward(cfg, w, toks, return_layers=True)
+    model_ = load_model(folder, dtype=dtype)
+    cache = CacheManager(model_.cache_needs, CacheConfig(num_pages=8, page_size=16, max_requests=2, dtype=model_.rt.dtype))
+    runner = ModelRunner(model_, cache, use_graphs=False)
+    seen = {}
+
+    def observer(i, x, pending):
+        if i != "final":
+            assert pending is None
+            seen[i] = x.detach().float().cpu().clone()
+
+    runner.observer = observer
+    cache.open("a")
+    runner.step([StepEntry("a", toks, [len(toks) - 1])])
+    assert sorted(seen) == list(range(len(cfg["layers"])))
+    for i in range(len(cfg["layers"])):
+        err = float(row_errors(seen[i], streams[i]).max())
+        assert err < (2e-5 if dtype == "float32" else 0.15), f"after layer run {i}: {err:.3g}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_far_tokens_reach_the_last_logits(tmp_path, dtype):
+    """A request of 700 tokens under windows of 40 and 64: what the last positions know of the first hundred tokens
+    comes through block means, kept positions and the delta rule's state only.  Decoded tokens and short portions far
+    into it, every cut against the plain model; and the plain model's last logits do move when an early token changes."""
+    from mini_hisparse_b200 import write_random_model
+
+    cfg = model(120, 128, [layer("attention", pooled(4, 2, 32, 32, 40, 8, rot=16), moe(4, 2, 64)),
+                           layer("attention_2", kept(4, 2, 32, 48, 64, 5, rot=32, factor=2.0), moe(4, 2, 64)),
+                           layer("delta", delta(4, 2, 32, 32, 4), moe(4, 2, 64))], mult=0.6)
+    write_random_model(cfg, 31, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
+    cfg, w = P.load_folder(tmp_path)
+    reqs = requests_for(cfg, [700], seed=70)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    changed = list(reqs["r0"])
+    changed[2] = (changed[2] + 1) % cfg["vocab"]
+    assert float(row_errors(P.forward(cfg, w, changed)[-1:].float(), refs["r0"][-1:])) > 25 * F32_ROW
+    whole = None
+    for steps in (S.whole(reqs), S.tail_one_by_one(reqs, tail=40), S.changing_portions(reqs, sizes=(530, 2, 7, 64, 3, 2))):
+        got, stats, pages = run_steps(tmp_path, dtype, steps)
+        check_against_plain(got, refs, dtype)
+        whole = whole or got
+        assert row_rms_error(got["r0"], whole["r0"]) < (F32_ROW if dtype == "float32" else BF16_CUT)
+
+
+def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
+    """A window one key off, a block size or a kept count one off, unscaled frequencies, heads that are not mixed, a
+    multiplier, a filter's tap, a layer that runs its own tensors instead of another's: each moves the plain model's
+    logits by far more than the float32 tolerance, so the comparisons above would show them."""
+    folder, cfg, w = models["A"]
+    toks = random_tokens(cfg["vocab"], 90, 5)
+    right = P.forward(cfg, w, toks)
+    rms = float(right.pow(2).mean().sqrt())
+
+    def moved(cfg2=None, w2=None):
+        return float((P.forward(cfg2 or cfg, w2 or w, toks) - right).pow(2).mean().sqrt()) / rms
+
+    changes = [lambda c: c["layers"][0]["mixer"]["mask"].update(size=21), lambda c: c["layers"][0]["mixer"]["mask"].update(size=19),
+               lambda c: c["layers"][0]["mixer"]["mask"].update(pool=5), lambda c: c["layers"][1]["mixer"]["mask"].update(size=25),
+               lambda c: c["layers"][1]["mixer"]["mask"].update(keep_first=2),
+               lambda c: c["layers"][1]["mixer"]["mask"].update(keep_first=4),
+               lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].update(factor=1.0),
+               lambda c: c["layers"][0]["mixer"]["rot"].update(dims=6), lambda c: c.update(residual_mult=0.6)]
+    for change in changes:
+        c = copy.deepcopy(cfg)
+        change(c)
+        assert moved(c) > 25 * F32_ROW
+    c = copy.deepcopy(cfg)                 # layer 3 with tensors of its own instead of layer 0's
+    c["layers"][3].pop("weights_of")
+    w2 = dict(w)
+    w2.update({k.replace("l0.", "l3.", 1): v * 0.9 for k, v in w.items() if k.startswith("l0.")})
+    assert moved(c, w2) > 25 * F32_ROW
+    c = copy.deepcopy(cfg)                 # layer 4 running the other delta layer's tensors
+    c["layers"][4] = dict(copy.deepcopy(c["layers"][6]), weights_of=6)
+    assert moved(c) > 25 * F32_ROW
+    for name, fn in (("l1.mix.talk", lambda t: torch.eye(t.shape[0], dtype=t.dtype)), ("l2.mix.q.conv", lambda t: t.flip(-1)),
+                     ("l0.mlp.router.b", lambda t: t * 0), ("l2.mix.dt_bias", lambda t: t + 1.0)):
+        w2 = dict(w)
+        w2[name] = fn(w[name])
+        assert moved(w2=w2) > 25 * F32_ROW
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_a_slot_used_again(models, dtype):
+    """A short prompt, then 260 tokens one by one (many windows, blocks and pages long), two requests side by side;
+    then their slots and pages serve new requests."""
+    folder, cfg, w = models["A"]
+    reqs = requests_for(cfg, [270, 265], seed=40)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = S.tail_one_by_one(reqs, tail=260, together=2)
+    again = requests_for(cfg, [50, 31], seed=60)
+    again = {f"again_{k}": v for k, v in again.items()}
+    refs.update({rid: P.forward(cfg, w, toks).float() for rid, toks in again.items()})
+    steps += S.changing_portions(again, sizes=(2, 29, 1, 7))
+    got, runner, cache = run_steps(folder, dtype, steps, max_requests=2)
+    check_against_plain(got, refs, dtype)
+    assert runner["graph_steps"] > 200
+
+
+def test_batches_of_unequal_requests_equal_each_alone(models):
+    """float32: a request's logits in a mixed batch equal those it gets alone, to rounding."""
+    folder, cfg, w = models["C"]
+    reqs = requests_for(cfg, [140, 3, 77, 30], seed=9)
+    alone, _, _ = run_steps(folder, "float32", S.whole(reqs), page_size=16)
+    mixed, _, _ = run_steps(folder, "float32", S.mixed(reqs, seed=11, tail=20), page_size=16)
+    for rid in reqs:
+        assert row_rms_error(mixed[rid], alone[rid]) < F32_ROW
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_engine(models, dtype):
+    """Engine.add_request / run: admission, portions under a token budget, decoding, finishing.  float32 tokens
+    equal the plain model's; in bfloat16 every token is the plain model's choice for the engine's own history,
+    or loses to it by less than rounding."""
+    from mini_hisparse_b200 import Engine, load_model
+
+    folder, cfg, w = models["A"]
+    model_ = load_model(folder, dtype=dtype)
+    engine = Engine(model_, num_pages=40, page_size=16, max_requests=3, max_tokens_per_step=48, graph_after=2)
+    prompts = requests_for(cfg, [70, 9, 33], seed=80)
+    for rid, p in prompts.items():
+        engine.add_request(rid, p, max_new_tokens=12)
+    out = engine.run()
+    engine.cache.assert_invariants()
+    for rid, p in prompts.items():
+        assert len(out[rid]) == 12
+        if dtype == "float32":
+            assert out[rid] == P.generate(cfg, w, p, 12)
+        else:
+            seq = list(p)
+            for tok in out[rid]:
+                logits = P.forward(cfg, w, seq)[-1]
+                assert float(logits.max() - logits[tok]) < 0.15 * float(logits.abs().max())
+                seq.append(tok)
+
+
+def test_command_line_demo_with_a_rizovik_config(capsys):
+    """`demo --config configs/rizovik-demo.json`: random weights, three requests through Engine and scheduler."""
+    from pathlib import Path
+
+    import mini_hisparse_b200
+    from mini_hisparse_b200 import cli
+
+    config = Path(mini_hisparse_b200.__file__).parent / "configs" / "rizovik-demo.json"
+    assert cli.main(["demo", "--config", str(config), "--dtype", "bfloat16", "--requests", "3", "--prompt-tokens", "70",
+                     "--max-new-tokens", "6"]) == 0
+    report = json.loads(capsys.readouterr().out)
+    assert [r["generated_tokens"] for r in report["requests"].values()] == [6, 6, 6]
+
+
+def test_trace_run_picks_the_model_by_its_config(models, tmp_path):
+    """bin/trace_run on a Rizovik folder: the same program, cache and step function as for every model."""
+    folder, cfg, w = models["B"]
+    reqs = requests_for(cfg, [60, 21], seed=90)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    steps = S.mixed(reqs, seed=1, tail=10)
+    run = TraceRun(folder, "float32", tmp_path / "out", S.peak_tokens(steps), page_size=16, extra=("--poison",))
+    got = {}
+    for entries, end in steps:
+        logits = run.step(entries, end)
+        row = 0
+        for e in entries:
+            got.setdefault(e["id"], []).append(logits[row: row + len(e["want"])])
+            row += len(e["want"])
+    assert run.close() == 0
+    check_against_plain({k: torch.cat(v) for k, v in got.items()}, refs, "float32")
