@@ -56,6 +56,12 @@ struct AttnArgs {
     int shared_kv;              // the values are the first dv elements of the key rows; a page holds those rows only
     int gate_per_head;          // the gate has one column per head instead of one per output element
     int out_f32;                // `out` is float32 (a sum of the outputs is still to be taken in 32 bits)
+    // keys that stay visible beyond the window, as in attention_simt.cu: pre_kind 1 = the first pre_n positions,
+    // 2 = the means of every block of pre_n positions that the window has passed wholly (from the pages' tails,
+    // pool_slots rows per KV head); they are walked as tiles of their own before the item's key range
+    int pre_kind, pre_n, pool_slots;
+    size_t page_extra;          // elements of a page behind its keys and values
+    int vhead;                  // >= 0: the values are those of this KV head, whatever the query head's own (-1: its own)
 };
 
 __device__ __forceinline__ void store_out(const AttnArgs& a, size_t idx, float v) {
@@ -130,7 +136,17 @@ attention_mma_kernel(const AttnArgs a) {
     const int k_ld = kparts * d_true;                    // a key row of one KV head: its maps side by side
     const int v_ld = shared_kv ? k_ld : dv_true;
     const size_t plane = shared_kv ? 0 : (size_t)a.nkv * a.P * k_ld;  // elements between the keys and the values of a page
-    const size_t page_elems = (size_t)a.nkv * a.P * k_ld + (shared_kv ? 0 : (size_t)a.nkv * a.P * dv_true);
+    const size_t kv_elems = (size_t)a.nkv * a.P * k_ld + (shared_kv ? 0 : (size_t)a.nkv * a.P * dv_true);
+    const size_t page_elems = kv_elems + (EXT ? a.page_extra : 0);
+    const int vh = (EXT && a.vhead >= 0) ? a.vhead : kvh;          // whose values
+    int pre_end = 0;                                               // keys (or block means) beyond the window
+    if constexpr (EXT) {
+        if (a.pre_kind && a.window > 0 && split <= 0 && nrows > 0) {
+            const int beyond = a.positions[tok0 + ntok - 1] - a.window + 1;    // the last row sees the most of them
+            if (beyond > 0) pre_end = a.pre_kind == 1 ? min(a.pre_n, beyond) : beyond / a.pre_n;
+        }
+    }
+    const int pre_tiles = (pre_end + KT - 1) / KT;
 
     // ---- stage the queries --------------------------------------------------------------------
     for (int c = tid; c < ROWS * (D / 8); c += THREADS) {
@@ -144,7 +160,11 @@ attention_mma_kernel(const AttnArgs a) {
 
     // Consecutive threads copy consecutive 16-byte chunks of a key row, so a warp's request covers
     // whole rows (full 32-byte sectors).  A thread meets KT * (D/8) / THREADS rows per tile.
-    auto load_tile = [&](int stage, int t0) {
+    auto load_tile = [&](int stage, int tile) {
+        const bool pre = tile < pre_tiles;
+        const int t0 = pre ? tile * KT : kv_begin + (tile - pre_tiles) * KT;
+        const int end = pre ? pre_end : kv_end;
+        const bool pooled = EXT && pre && a.pre_kind == 2;
         constexpr int CPR = D / 8 + DV / 8;                // chunks per position: its key, then its value
         constexpr int ITERS = KT * CPR / THREADS;
         const uint32_t kbase = kv_s + stage * (L::K_BYTES + L::V_BYTES);
@@ -157,31 +177,44 @@ attention_mma_kernel(const AttnArgs a) {
             const int j = c / CPR, ch = c % CPR;
             const int kp = t0 + j;
             int page = -1;
-            if (kp < kv_end) {
-                page = table[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.P)];
+            int within = a.page_shift >= 0 ? (kp & (a.P - 1)) : (kp % a.P);
+            if (kp < end) {
+                if (pooled) {          // block kp lies in the page of its last position
+                    const int pg = (kp * a.pre_n + a.pre_n - 1) / a.P;
+                    within = kp - (int)(((long long)pg * a.P) / a.pre_n);
+                    page = table[pg];
+                } else {
+                    page = table[a.page_shift >= 0 ? (kp >> a.page_shift) : (kp / a.P)];
+                }
                 if (page >= a.num_pages) page = -1;
             }
-            const int within = a.page_shift >= 0 ? (kp & (a.P - 1)) : (kp % a.P);
             const __nv_bfloat16* src = a.cache;
             int bytes = page >= 0 ? 16 : 0;
             if (ch < D / 8) {
                 if (ch * 8 >= d_true) bytes = 0;           // the tile's tail beyond the true width stays zero
-                if (bytes) src += (size_t)page * page_elems + ((size_t)kvh * a.P + within) * k_ld + map * d_true + ch * 8;
+                if (bytes) {
+                    if (pooled) src += (size_t)page * page_elems + kv_elems + ((size_t)kvh * a.pool_slots + within) * d_true + ch * 8;
+                    else src += (size_t)page * page_elems + ((size_t)kvh * a.P + within) * k_ld + map * d_true + ch * 8;
+                }
                 cp_async16(kbase + (j * LD + ch * 8) * 2, src, bytes);
             } else {
                 const int cv = ch - D / 8;
                 if (cv * 8 >= dv_true) bytes = 0;
-                if (bytes) src += (size_t)page * page_elems + plane + ((size_t)kvh * a.P + within) * v_ld + cv * 8;
+                if (bytes) {
+                    if (pooled) src += (size_t)page * page_elems + kv_elems + (size_t)a.nkv * a.pool_slots * d_true +
+                                       ((size_t)vh * a.pool_slots + within) * dv_true + cv * 8;
+                    else src += (size_t)page * page_elems + plane + ((size_t)vh * a.P + within) * v_ld + cv * 8;
+                }
                 cp_async16(vbase + (j * LDV + cv * 8) * 2, src, bytes);
             }
         }
     };
 
     constexpr int STAGES = L::STAGES;
-    const int ntiles = (kv_end - kv_begin + KT - 1) / KT;
+    const int ntiles = pre_tiles + (kv_end - kv_begin + KT - 1) / KT;
 #pragma unroll 1
     for (int st = 0; st < STAGES - 1; ++st) {
-        if (st < ntiles) load_tile(st, kv_begin + st * KT);
+        if (st < ntiles) load_tile(st, st);
         cp_async_commit();
     }
 
@@ -211,7 +244,7 @@ attention_mma_kernel(const AttnArgs a) {
     for (int itile = 0; itile < ntiles; ++itile) {
         const int stage = itile % STAGES;
         if (itile + STAGES - 1 < ntiles)
-            load_tile((itile + STAGES - 1) % STAGES, kv_begin + (itile + STAGES - 1) * KT);
+            load_tile((itile + STAGES - 1) % STAGES, itile + STAGES - 1);
         cp_async_commit();
         cp_async_wait<STAGES - 1>();
         __syncthreads();
@@ -224,7 +257,8 @@ attention_mma_kernel(const AttnArgs a) {
         }
         const uint32_t k_s = kv_s + stage * (L::K_BYTES + L::V_BYTES);
         const uint32_t v_s = k_s + L::K_BYTES;
-        const int t0 = kv_begin + itile * KT;
+        const bool pre = itile < pre_tiles;
+        const int t0 = pre ? itile * KT : kv_begin + (itile - pre_tiles) * KT;
         const int key0 = SPLIT_KEYS ? warp * 16 : 0;      // first key of this warp inside the tile
 
         // ---- S = Q K^T -------------------------------------------------------------------------
@@ -270,6 +304,16 @@ attention_mma_kernel(const AttnArgs a) {
         }
         // ---- mask, online softmax -----------------------------------------------------------------
         float mx[2] = {-INFINITY, -INFINITY};
+        int pre_lim[2] = {0, 0};          // in a tile of keys beyond the window: how many of them each of the two rows sees
+        if constexpr (EXT) {
+            if (pre) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int beyond = row_pos[wrow + (lane >> 2) + 8 * h] - a.window + 1;
+                    pre_lim[h] = beyond <= 0 ? 0 : (a.pre_kind == 1 ? min(a.pre_n, beyond) : beyond / a.pre_n);
+                }
+            }
+        }
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
 #pragma unroll
@@ -277,7 +321,8 @@ attention_mma_kernel(const AttnArgs a) {
                 const int row = wrow + (lane >> 2) + 8 * (x >> 1);
                 const int kp = t0 + key0 + j * 8 + (lane & 3) * 2 + (x & 1);
                 const int qp = row_pos[row];
-                const bool valid = kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
+                bool valid = kp < kv_end && kp <= qp && (a.window <= 0 || kp > qp - a.window);
+                if (EXT && pre) valid = kp < pre_lim[x >> 1];
                 s[j][x] = valid ? s[j][x] : -INFINITY;
                 mx[x >> 1] = fmaxf(mx[x >> 1], s[j][x]);
             }
@@ -523,5 +568,6 @@ inline void fill_args(AttnArgs& a, const void* q, const void* cache, void* out, 
     if (P > 0 && (P & (P - 1)) == 0) { a.page_shift = 0; while ((1 << a.page_shift) < P) ++a.page_shift; }
     a.d = a.dv = 0; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
     a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
+    a.pre_kind = 0; a.pre_n = 0; a.pool_slots = 0; a.page_extra = 0; a.vhead = -1;
 }
 }  // namespace mhb_amma

@@ -9,8 +9,9 @@
 //                completes a block writes it (it runs behind the kernel that appended this step's rows); the
 //                others return at once.
 //   talk_mix     o[t][h][:] = sum_g talk[h][g] a[t][g][kv(h)][:]: the heads' softmax weights mixed AFTER the
-//                softmax, written as a mix of outputs: a[t][g] is head g's weights applied to the values of every
-//                KV head ([nkv][dv] wide), and head h keeps the values of its own KV head.
+//                softmax, written as a mix of outputs: a[t][g][c] is head g's weights applied to the values of KV
+//                head c, and head h keeps the values of its own KV head.  The three strides of `a` (token, head,
+//                KV head) are arguments: one kernel writes rows [nkv][dv] wide, another one plane per KV head.
 #include "common.cuh"
 
 using namespace mhb;
@@ -60,17 +61,17 @@ pool_means_kernel(CT* __restrict__ cache, const int* __restrict__ positions, con
 
 template <typename OT>
 __global__ void __launch_bounds__(256)
-talk_mix_kernel(const float* __restrict__ a, const float* __restrict__ talk, OT* __restrict__ out, int nq, int nkv, int dv) {
+talk_mix_kernel(const float* __restrict__ a, const float* __restrict__ talk, OT* __restrict__ out, int nq, int nkv, int dv,
+                size_t tok_stride, size_t head_stride, size_t kv_stride) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const int groups = nq / nkv;
-    const size_t row = (size_t)nkv * dv;
     for (int idx = threadIdx.x; idx < nq * dv; idx += blockDim.x) {
         const int h = idx / dv, e = idx - h * dv;
-        const float* src = a + (size_t)t * nq * row + (size_t)(h / groups) * dv + e;
+        const float* src = a + (size_t)t * tok_stride + (size_t)(h / groups) * kv_stride + e;
         float o = 0.f;
-        for (int g = 0; g < nq; ++g) o = fmaf(talk[h * nq + g], src[(size_t)g * row], o);
+        for (int g = 0; g < nq; ++g) o = fmaf(talk[h * nq + g], src[(size_t)g * head_stride], o);
         out[(size_t)t * nq * dv + idx] = from_float<OT>(o);
     }
 }
@@ -88,10 +89,11 @@ MHB_EXPORT int mhb_pool_means(void* cache, int dtype, const int* positions, cons
 }
 
 MHB_EXPORT int mhb_talk_mix(const float* a, const float* talk, void* out, int dtype, int T, int nq, int nkv, int dv,
-                            cudaStream_t stream) {
+                            long long tok_stride, long long head_stride, long long kv_stride, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (nkv < 1 || nq % nkv) return fail("talk_mix: %d heads over %d KV heads", nq, nkv);
     MHB_DISPATCH_DTYPE(dtype, OT,
-        launch_kernel(talk_mix_kernel<OT>, dim3(T), dim3(256), 0, stream, a, talk, (OT*)out, nq, nkv, dv));
+        launch_kernel(talk_mix_kernel<OT>, dim3(T), dim3(256), 0, stream, a, talk, (OT*)out, nq, nkv, dv,
+                      (size_t)tok_stride, (size_t)head_stride, (size_t)kv_stride));
     return check_launch("talk_mix");
 }

@@ -559,11 +559,13 @@ def attention_mma_ext_supports(d: int, dv: int) -> bool:
 def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, positions, block_table,
                       tok_part_row, *, nq, nkv, d, dv, page_size, window=0, scale=None, tok_nsplit=None,
                       counters=None, sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, kparts=1, softcap=0.0,
-                      shared_kv=False, gate_per_head=False):
+                      shared_kv=False, gate_per_head=False, keep_first=0, pool=0, value_head=None):
     """attention_mma with the options of attention_simt: values ``dv`` wide in pages that hold the keys of
     all KV heads followed by their values, a ``sink`` per query head, a ``gate`` on the output; the softmax's
     weights enter the value product as two bfloat16 numbers each (16 bits instead of 8).  ``kparts``,
-    ``softcap``, ``shared_kv`` and ``gate_per_head`` as in attention_simt; ``out`` may be float32."""
+    ``softcap``, ``shared_kv``, ``gate_per_head``, ``keep_first`` and ``pool`` as in attention_simt; ``out`` may be
+    float32.  ``value_head``: every query head's weights are applied to the values of that one KV head (a mixer
+    that mixes the heads' weights calls once per KV head)."""
     lib = build.load("attention_mma_ext")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_mma_ext: q and the (contiguous) pool must be bfloat16")
@@ -572,6 +574,20 @@ def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
     if scale is None:
         scale = float(d) ** -0.5
     g = _gate_args(gate, gate_nsplit, gate_split_stride)
+    if keep_first or pool or value_head is not None:
+        if keep_first and pool:
+            raise KernelError("attention: kept first positions or pooled blocks, not both")
+        if kparts != 1 or softcap or shared_kv or gate_per_head or sink is not None:
+            raise KernelError("attention: keys beyond the window go with plain keys and values only")
+        _check(lib, lib.mhb_attention_mma_masked(
+            _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
+            c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
+            _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d), c_int(dv),
+            c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), g[0], g[1], g[2], g[3],
+            c_int(1 if out.dtype == torch.float32 else 0), c_int(1 if keep_first else 2 if pool else 0),
+            c_int(keep_first or pool or 0), c_int(-1 if value_head is None else value_head), _stream()),
+            "attention_mma_ext")
+        return
     _check(lib, lib.mhb_attention_mma_ext(
         _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
         c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
@@ -1133,17 +1149,19 @@ def pool_means(cache, positions, tok_seg, block_table, *, nkv, d, dv, page_size,
                                    _stream()), "pool_means")
 
 
-def talk_mix(a, talk, out, *, nq, nkv, dv):
-    """out[t, h] = sum_g talk[h, g] * a[t, g, kv(h)]: ``a`` float32 [T, nq, nkv * dv] (every head's weights over the
-    values of every KV head), ``talk`` float32 [nq, nq], ``out`` [T, nq * dv]."""
+def talk_mix(a, talk, out, *, nq, nkv, dv, planes=False):
+    """out[t, h] = sum_g talk[h, g] * a[t, g, kv(h)]: ``a`` float32 holds every head's weights over the values of
+    every KV head, as rows [T, nq, nkv * dv] or (``planes``) as one matrix per KV head, [nkv, T, nq, dv]; ``talk``
+    float32 [nq, nq]; ``out`` [T, nq * dv]."""
     lib = build.load("maskparts")
     T = out.shape[0]
     if a.dtype != torch.float32 or not a.is_contiguous() or a.numel() != T * nq * nkv * dv or not out.is_contiguous():
-        raise KernelError("talk_mix: a is contiguous float32 [T, nq, nkv * dv], out contiguous")
+        raise KernelError("talk_mix: a is contiguous float32 with T * nq * nkv * dv numbers, out contiguous")
     if talk.dtype != torch.float32 or tuple(talk.shape) != (nq, nq) or not talk.is_contiguous():
         raise KernelError(f"talk_mix: the mixing matrix is contiguous float32 [{nq}, {nq}]")
+    strides = (nq * dv, dv, T * nq * dv) if planes else (nq * nkv * dv, nkv * dv, dv)
     _check(lib, lib.mhb_talk_mix(_ptr(a), _ptr(talk), _ptr(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(nq),
-                                 c_int(nkv), c_int(dv), _stream()), "talk_mix")
+                                 c_int(nkv), c_int(dv), *(c_longlong(x) for x in strides), _stream()), "talk_mix")
 
 
 # ---- the gated delta rule (csrc/deltarule.cu) -------------------------------------------------------------------

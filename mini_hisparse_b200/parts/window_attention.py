@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api as K
-from .attention import ROW_TILE, AttentionPlanner, AttentionShape
+from .attention import ITEM_INTS, ROW_TILE, AttentionPlanner, AttentionShape
 from .base import CacheView, Mixer, Product, StepContext
 from .multimap_attention import _pad_rows
 from .registry import POSITIONS, register_mixer
@@ -43,14 +43,24 @@ class WindowAttentionBase(Mixer):
         self.qw, self.kw, self.vw, self.ow = self.nq * self.dk, self.nkv * self.dk, self.nkv * self.dv, self.nq * self.dv
         self.weight = self.o_weight = self.q_norm = self.k_norm = None
 
+    def kernel_family(self) -> str:
+        """"mma": mma.sync tiles of 64 rows for long portions and of 16 rows for decoded tokens and short portions
+        (bfloat16, widths that are multiples of 8 up to 128); "simt": the CUDA cores (float32, and every other width)."""
+        if self.rt is None or self.rt.dtype != torch.bfloat16 or not K.attention_mma_ext_supports(self.dk, self.dv):
+            return "simt"
+        return "mma"
+
     def kernel_modules(self):
-        return ("attention_simt", "postnorm", "maskparts")
+        if self.kernel_family() == "simt":
+            return ("attention_simt", "postnorm", "maskparts")
+        return ("attention_simt", "attention_mma_ext", "postnorm", "maskparts")
 
     def plan_key(self):
         return (self.spec.kind, self.nq, self.nkv, self.window)
 
     def planner(self, page_size: int, sm_count: int):
-        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, ROW_TILE), sm_count)
+        rows = 64 if self.kernel_family() == "mma" else ROW_TILE
+        return AttentionPlanner(AttentionShape(self.nq, self.nkv, self.window, rows), sm_count)
 
     def _norm_shapes(self):
         return ((self.dk,), (self.dk,)) if self.per_head_norm else ((self.qw,), (self.kw,))
@@ -69,6 +79,25 @@ class WindowAttentionBase(Mixer):
                              split_stride=proj.split_stride, status=ctx.status, per_head=self.per_head_norm,
                              v_eps=v_eps, page_extra=page_extra)
         return proj, q
+
+    def _attend_mma(self, q, out, ctx: StepContext, cache: CacheView, **options):
+        """The plan's items on the tensor cores: 16-row tiles whose key splits the last CTA merges, 64-row tiles."""
+        ws, meta, T = ctx.ws, cache.meta, q.shape[0]
+        part_rows = max(1, meta["part_rows_cap"])
+        part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.dv), torch.float32)
+        part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
+        n_small, n_big = meta["n_small"], meta["n_big"]
+        args = (q, cache.storage, out, part_acc, part_ml)
+        tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
+        common = dict(nq=self.nq, nkv=self.nkv, d=self.dk, dv=self.dv, page_size=cache.page_size, window=self.window,
+                      scale=self.scale, **options)
+        if n_small:
+            chunks = -(-(self.nq // self.nkv) // ROW_TILE)
+            counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
+            K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common, tok_nsplit=meta["tok_nsplit"],
+                                counters=counters)
+        if n_big:
+            K.attention_mma_ext(*args, meta["items"][n_small * ITEM_INTS:], n_big, 64, *tail, **common)
 
     def _attend(self, q, out, width, ctx: StepContext, cache: CacheView, **options):
         """The plan's items on the CUDA cores and the merge of split tokens; ``width`` is an output row's."""
@@ -136,8 +165,12 @@ class PooledWindowAttention(WindowAttentionBase):
         p = proj.tensor
         g0 = self.qw + self.kw + self.vw
         attn = ws.get("wa_attn", (T, self.ow), rt.dtype)
-        self._attend(q, attn, self.dv, ctx, cache, pool=self.pool, gate=(p[0] if proj.nsplit > 1 else p)[:, g0:g0 + self.ow],
-                     gate_nsplit=proj.nsplit, gate_split_stride=proj.split_stride)
+        gate = dict(gate=(p[0] if proj.nsplit > 1 else p)[:, g0:g0 + self.ow], gate_nsplit=proj.nsplit,
+                    gate_split_stride=proj.split_stride)
+        if self.kernel_family() == "mma":
+            self._attend_mma(q, attn, ctx, cache, pool=self.pool, **gate)
+        else:
+            self._attend(q, attn, self.dv, ctx, cache, pool=self.pool, **gate)
         return rt.linear(attn, self.o_weight, ws, "mix_out", out_dtype=torch.float32)
 
 
@@ -162,9 +195,9 @@ class KeptFirstAttention(WindowAttentionBase):
         self.keep_first = int(spec["keep_first"])
         if self.keep_first < 0:
             raise ValueError("keep_first cannot be negative")
-        if self.nkv * self.dv > 512:
-            raise ValueError(f"values of {self.nkv} KV heads x {self.dv}: the kernel that applies every head's weights "
-                             "to all of them takes up to 512")
+        if self.kernel_family() == "simt" and self.nkv * self.dv > 512:
+            raise ValueError(f"values of {self.nkv} KV heads x {self.dv}: the CUDA-core kernel that applies every head's "
+                             "weights to all of them takes up to 512")
         self.talk = None
 
     def cache_need(self):
@@ -191,8 +224,15 @@ class KeptFirstAttention(WindowAttentionBase):
         rt, ws, T = ctx.rt, ctx.ws, h.shape[0]
         _, q = self._project(h, ctx, cache)
         wide = self.nkv * self.dv
-        every = ws.get("wa_every", (T, self.nq, wide), torch.float32)
-        self._attend(q, every, wide, ctx, cache, keep_first=self.keep_first, all_values=True)
         attn = ws.get("wa_attn", (T, self.ow), rt.dtype)
-        K.talk_mix(every, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv)
+        if self.kernel_family() == "mma":
+            # one pass per KV head: every query head's weights over that head's values, a plane of outputs each
+            planes = ws.get("wa_every", (self.nkv, T, self.nq, self.dv), torch.float32)
+            for c in range(self.nkv):
+                self._attend_mma(q, planes[c], ctx, cache, keep_first=self.keep_first, value_head=c)
+            K.talk_mix(planes, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv, planes=True)
+        else:
+            every = ws.get("wa_every", (T, self.nq, wide), torch.float32)
+            self._attend(q, every, wide, ctx, cache, keep_first=self.keep_first, all_values=True)
+            K.talk_mix(every, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv)
         return rt.linear(attn, self.o_weight, ws, "mix_out", out_dtype=torch.float32)

@@ -95,14 +95,14 @@ PAGES = {"A": 16, "B": 8, "C": 32}
 # model is computed in float64; the design computed in float32 in any order differs from that by some 1e-6 on average
 # and by more at single positions (a sublayer's result that nearly cancels is normalised right after).  bfloat16: the
 # router sees the bfloat16 rounding of its input, so that at some tokens another expert wins a close call than in
-# the plain model.  These models have a router in nearly every layer over a handful of experts, and every sublayer's
-# result is normalised before it is added, so such a token's row differs as a whole, and through the caches and states
-# a little of that reaches every later token of its request (a handful of tokens out of the five hundred of a run):
-# the mean over all rows and the worst row are held loosely against the plain model, every schedule is compared with
-# the WHOLE prompt in the same dtype as well, and the float32 runs hold the same code to 1.5e-4.
-BF16_MEAN, BF16_WORST = 0.12, 1.6
+# the plain model.  These models have a router in nearly every layer over a handful of experts (one layer takes one
+# expert of four), and every sublayer's result is normalised before it is added, so such a token's row differs as a
+# whole, and through the caches and states a little of that reaches every later token of its request.  So in bfloat16
+# the MEDIAN row is held tightly (a fault in a kernel moves all rows), the share of rows that are far off is bounded,
+# every schedule is compared with the WHOLE prompt in the same dtype in the same way, and the float32 runs hold the
+# same code to 1.5e-4 row by row.
+BF16_MEDIAN, BF16_FAR, BF16_FAR_SHARE = 0.04, 0.3, 0.15
 F32_MEAN, F32_ROW = 1.5e-5, 1.5e-4
-BF16_CUT = 0.5
 
 
 @pytest.fixture(scope="module")
@@ -128,10 +128,17 @@ def row_errors(got, ref):
 def check_against_plain(got, refs, dtype):
     for rid, ref in refs.items():
         assert got[rid].shape == ref.shape
-    err = torch.cat([row_errors(got[rid], ref) for rid, ref in refs.items()])
-    mean, worst = (F32_MEAN, F32_ROW) if dtype == "float32" else (BF16_MEAN, BF16_WORST)
-    assert float(err.mean()) < mean and float(err.max()) < worst, \
-        f"mean row error {float(err.mean()):.3g}, worst {float(err.max()):.3g} at {int(err.argmax())} of all rows"
+    check_rows(torch.cat([row_errors(got[rid], ref) for rid, ref in refs.items()]), dtype)
+
+
+def check_rows(err, dtype):
+    if dtype == "float32":
+        assert float(err.mean()) < F32_MEAN and float(err.max()) < F32_ROW, \
+            f"mean row error {float(err.mean()):.3g}, worst {float(err.max()):.3g} at {int(err.argmax())} of all rows"
+    else:
+        far = float((err > BF16_FAR).double().mean())
+        assert float(err.median()) < BF16_MEDIAN and far < BF16_FAR_SHARE, \
+            f"median row error {float(err.median()):.3g}, {far:.3g} of the rows beyond {BF16_FAR}"
 
 
 def close(got, ref, tol, what=""):
@@ -184,13 +191,15 @@ class Pool:
         return out
 
 
-def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_dtype, split_sms=148, **opts):
-    """Plan the step's attention for one request's segments and run the CUDA-core kernel and the merge."""
+def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_dtype, split_sms=148, kernel="simt",
+                  **opts):
+    """Plan the step's attention for one request's segments and run the CUDA-core kernel and the merge, or the
+    tensor-core kernel (16-row tiles whose last CTA merges a token's key splits, 64-row tiles)."""
     from mini_hisparse_b200.kernels import api as K
     from mini_hisparse_b200.parts.attention import AttentionShape, plan_attention
 
     T = sum(s.count for s in segments)
-    plan = plan_attention(AttentionShape(nq, pool_.G, window, 16), segments, T, sm_count=split_sms)
+    plan = plan_attention(AttentionShape(nq, pool_.G, window, 64 if kernel == "mma" else 16), segments, T, sm_count=split_sms)
     n = plan.n_small + plan.n_big
     part_acc = torch.empty(max(1, plan.part_rows), nq, out_width, device="cuda")
     part_ml = torch.empty(max(1, plan.part_rows), nq, 2, device="cuda")
@@ -198,6 +207,18 @@ def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_
     tables = dev_i(pool_.table[None, :].repeat(len(segments), 1))
     positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
     tpr, tns = dev_i(torch.from_numpy(plan.tok_part_row)), dev_i(torch.from_numpy(plan.tok_nsplit))
+    if kernel == "mma":
+        items = dev_i(torch.from_numpy(plan.items)).view(-1)
+        common = dict(nq=nq, nkv=pool_.G, d=pool_.d, dv=pool_.dv, page_size=pool_.P, window=window, scale=scale, **opts)
+        if plan.n_small:
+            counters = torch.zeros(T * pool_.G * -(-(nq // pool_.G) // 16), dtype=torch.int32, device="cuda")
+            K.attention_mma_ext(q_rows, pool_.storage, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables,
+                                tpr, **common, tok_nsplit=tns, counters=counters)
+            assert int(counters.abs().sum()) == 0
+        if plan.n_big:
+            K.attention_mma_ext(q_rows, pool_.storage, o, part_acc, part_ml, items[plan.n_small * 8:], plan.n_big, 64,
+                                positions, tables, tpr, **common)
+        return o.float().cpu().double(), plan
     K.attention_simt(q_rows, pool_.storage, o, part_acc, part_ml, dev_i(torch.from_numpy(plan.items)), n, n, positions,
                      tables, tpr, nq=nq, nkv=pool_.G, d=pool_.d, dv=pool_.dv, page_size=pool_.P, window=window,
                      scale=scale, **opts)
@@ -311,14 +332,16 @@ def standing_out(k, q_row, at, strength=14.0):
 @pytest.mark.parametrize("H,G,d,dv,P_,size,pool,L", [(4, 2, 24, 40, 16, 20, 4, 150), (1, 1, 20, 20, 8, 7, 5, 90),
                                                      (3, 3, 12, 8, 8, 1, 1, 40), (8, 2, 64, 64, 32, 96, 16, 700),
                                                      (2, 1, 16, 24, 7, 10, 3, 64)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_window_with_pooled_blocks(H, G, d, dv, P_, size, pool, L, dtype):
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+def test_window_with_pooled_blocks(H, G, d, dv, P_, size, pool, L, dtype, kernel):
     """The last query of a prompt portion, of a portion of three and a decoded token each get one key that stands
     out: the oldest position inside the window, the position right before it (seen only once its block is pooled), a
     position of the newest pooled block, one of the block that is not pooled yet, and one far back.  The kernel's
     output follows the plain function in every case, with a gate on the output, key splits or none."""
     from mini_hisparse_b200.kernels import api as K
 
+    if kernel == "mma" and (d % 8 or dv % 8):
+        pytest.skip("the tensor-core tiles take widths that are multiples of 8")
     g = torch.Generator().manual_seed(H * d + L)
     scale = 0.25
     spans = [(L - 41, 30), (L - 11, 3), (L - 8, 1), (L - 7, 2), (L - 5, 1), (L - 4, 4)]
@@ -346,7 +369,8 @@ def test_window_with_pooled_blocks(H, G, d, dv, P_, size, pool, L, dtype):
         ref = ref * torch.sigmoid(gate[:, 2:2 + H * dv].double()).view(T, H, dv)
         for sms in (148, 100000):                          # as planned for this GPU, and with every short segment split
             got, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=dv,
-                                      out_dtype=dtype, split_sms=sms, pool=pool, gate=gate.cuda()[:, 2:2 + H * dv])
+                                      out_dtype=dtype, split_sms=sms, kernel=kernel, pool=pool,
+                                      gate=gate.cuda()[:, 2:2 + H * dv])
             close(got, ref, 3e-6 if dtype == torch.float32 else 0.012, f"{case}, {plan.part_rows} partial rows")
         if case == "window_out" and pool > 1:     # the plain function itself tells a window one position wider apart
             other = P.pooled_window_softmax(qd.cpu().double(), kc, vc, scale, size + 1, pool, qpos=qpos)
@@ -356,13 +380,15 @@ def test_window_with_pooled_blocks(H, G, d, dv, P_, size, pool, L, dtype):
 @pytest.mark.parametrize("H,G,d,dv,P_,size,keep,L", [(6, 3, 16, 24, 16, 24, 3, 150), (1, 1, 12, 20, 8, 5, 0, 60),
                                                      (2, 2, 20, 12, 8, 9, 1, 70), (4, 2, 128, 128, 32, 64, 4, 600),
                                                      (4, 1, 32, 16, 7, 6, 9, 50)])
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_window_with_kept_first_positions_and_mixed_heads(H, G, d, dv, P_, size, keep, L, dtype):
+@pytest.mark.parametrize("dtype,kernel", [(torch.float32, "simt"), (torch.bfloat16, "simt"), (torch.bfloat16, "mma")])
+def test_window_with_kept_first_positions_and_mixed_heads(H, G, d, dv, P_, size, keep, L, dtype, kernel):
     """One key stands out for the last rows of a portion, of a short portion and of decoded tokens: the last kept
     position, the first one that is not kept, the window's oldest position and the one before it.  Every head's
     weights go over the values of all KV heads; the mix of the heads follows."""
     from mini_hisparse_b200.kernels import api as K
 
+    if kernel == "mma" and (d % 8 or dv % 8):
+        pytest.skip("the tensor-core tiles take widths that are multiples of 8")
     g = torch.Generator().manual_seed(H * d + L)
     scale = 0.25
     spans = [(L - 41, 30), (L - 11, 3), (L - 8, 1), (L - 7, 2), (L - 5, 1), (L - 4, 4)]
@@ -384,10 +410,16 @@ def test_window_with_kept_first_positions_and_mixed_heads(H, G, d, dv, P_, size,
         qd = q.to(dtype).cuda()
         ref = P.kept_first_mixed(qd.cpu().double(), kc, vc, talk.double(), scale, size, keep, qpos=qpos)
         for sms in (148, 100000):
-            wide, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=G * dv,
-                                       out_dtype=torch.float32, split_sms=sms, keep_first=keep, all_values=True)
             out = torch.empty(T, H * dv, dtype=dtype, device="cuda")
-            K.talk_mix(wide.float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv)
+            if kernel == "mma":       # one pass per KV head, a plane of outputs each
+                planes = [run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=dv,
+                                        out_dtype=torch.float32, split_sms=sms, kernel="mma", keep_first=keep,
+                                        value_head=c)[0] for c in range(G)]
+                K.talk_mix(torch.stack(planes).float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv, planes=True)
+            else:
+                wide, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=G * dv,
+                                           out_dtype=torch.float32, split_sms=sms, keep_first=keep, all_values=True)
+                K.talk_mix(wide.float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv)
             close(out.float().view(T, H, dv), ref, 3e-6 if dtype == torch.float32 else 0.012, case)
         if case in ("first_out", "window_out") and keep + size + 2 < L - 41:
             other = P.kept_first_mixed(qd.cpu().double(), kc, vc, talk.double(), scale, size + (case == "window_out"),
@@ -542,8 +574,7 @@ def test_every_schedule_agrees_with_the_plain_model(models, name, dtype):
         got, runner, cache = run_steps(folder, dtype, steps, page_size=PAGES[name])
         check_against_plain(got, refs, dtype)
         whole = whole or got
-        worst = max(row_rms_error(got[rid], whole[rid]) for rid in reqs)
-        assert worst < (F32_ROW if dtype == "float32" else BF16_CUT)
+        check_rows(torch.cat([row_errors(got[rid], whole[rid]) for rid in reqs]), dtype)
     assert all(g["pages_reused"] > 0 for g in cache["page_groups"])
 
 
@@ -571,8 +602,9 @@ def test_the_stream_after_every_layer(models, dtype):
     runner.step([StepEntry("a", toks, [len(toks) - 1])])
     assert sorted(seen) == list(range(len(cfg["layers"])))
     for i in range(len(cfg["layers"])):
-        err = float(row_errors(seen[i], streams[i]).max())
-        assert err < (2e-5 if dtype == "float32" else 0.15), f"after layer run {i}: {err:.3g}"
+        err = row_errors(seen[i], streams[i])
+        err = float(err.max() if dtype == "float32" else err.median())       # bfloat16: single rows take another expert
+        assert err < (2e-5 if dtype == "float32" else 0.03), f"after layer run {i}: {err:.3g}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -597,7 +629,7 @@ def test_far_tokens_reach_the_last_logits(tmp_path, dtype):
         got, stats, pages = run_steps(tmp_path, dtype, steps)
         check_against_plain(got, refs, dtype)
         whole = whole or got
-        assert row_rms_error(got["r0"], whole["r0"]) < (F32_ROW if dtype == "float32" else BF16_CUT)
+        check_rows(row_errors(got["r0"], whole["r0"]), dtype)
 
 
 def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
@@ -667,8 +699,8 @@ def test_batches_of_unequal_requests_equal_each_alone(models):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_greedy_generation_through_the_engine(models, dtype):
     """Engine.add_request / run: admission, portions under a token budget, decoding, finishing.  float32 tokens
-    equal the plain model's; in bfloat16 every token is the plain model's choice for the engine's own history,
-    or loses to it by less than rounding."""
+    equal the plain model's; in bfloat16 nearly every token is the plain model's choice for the engine's own history,
+    or loses to it by less than rounding (a token whose row took another expert may not be)."""
     from mini_hisparse_b200 import Engine, load_model
 
     folder, cfg, w = models["A"]
@@ -679,6 +711,7 @@ def test_greedy_generation_through_the_engine(models, dtype):
         engine.add_request(rid, p, max_new_tokens=12)
     out = engine.run()
     engine.cache.assert_invariants()
+    near = []
     for rid, p in prompts.items():
         assert len(out[rid]) == 12
         if dtype == "float32":
@@ -687,8 +720,9 @@ def test_greedy_generation_through_the_engine(models, dtype):
             seq = list(p)
             for tok in out[rid]:
                 logits = P.forward(cfg, w, seq)[-1]
-                assert float(logits.max() - logits[tok]) < 0.15 * float(logits.abs().max())
+                near.append(float(logits.max() - logits[tok]) < 0.05 * float(logits.abs().max()))
                 seq.append(tok)
+    assert dtype == "float32" or sum(near) >= 0.8 * len(near)
 
 
 def test_command_line_demo_with_a_rizovik_config(capsys):
