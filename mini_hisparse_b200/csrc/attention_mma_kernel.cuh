@@ -62,6 +62,10 @@ struct AttnArgs {
     int pre_kind, pre_n, pool_slots;
     size_t page_extra;          // elements of a page behind its keys and values
     int vhead;                  // >= 0: the values are those of this KV head, whatever the query head's own (-1: its own)
+    // vplanes > 0: gridDim.z = vplanes, and the CTAs of plane z take the values of KV head z and write a plane of their
+    // own of the output, of the partial buffers and of the merge counters
+    int vplanes;
+    size_t out_plane, part_plane_rows, counters_plane;
 };
 
 __device__ __forceinline__ void store_out(const AttnArgs& a, size_t idx, float v) {
@@ -104,7 +108,18 @@ struct Layout {
 // of the key rows (a latent cache), a.gate_per_head reads one gate per head, a.out_f32 writes float32.
 template <int D, int DV, int ROWS, bool EXT>
 __global__ void __launch_bounds__(THREADS)
-attention_mma_kernel(const AttnArgs a) {
+attention_mma_kernel(const AttnArgs a_in) {
+    AttnArgs a = a_in;
+    if constexpr (EXT) {
+        if (a.vplanes > 0) {
+            const size_t z = blockIdx.z;
+            a.vhead = (int)z;
+            a.out = a.out_f32 ? (__nv_bfloat16*)((float*)a.out + z * a.out_plane) : a.out + z * a.out_plane;
+            a.part_acc += z * a.part_plane_rows * a.nq * a.dv;
+            a.part_ml += z * a.part_plane_rows * a.nq * 2;
+            if (a.counters) a.counters += z * a.counters_plane;
+        }
+    }
     using L = Layout<D, DV, ROWS>;
     constexpr int LD = L::LD, LDV = L::LDV;
     constexpr int KSTEPS = D / 16;        // k-steps of Q K^T
@@ -550,7 +565,7 @@ int launch(const AttnArgs& a, int launch_items, cudaStream_t stream) {
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
-    dim3 grid(launch_items, a.nkv * (EXT ? a.kparts : 1));
+    dim3 grid(launch_items, a.nkv * (EXT ? a.kparts : 1), EXT && a.vplanes > 0 ? a.vplanes : 1);
     launch_kernel(kern, grid, dim3(THREADS), smem, stream, a);
     return check_launch("attention_mma");
 }
@@ -569,5 +584,6 @@ inline void fill_args(AttnArgs& a, const void* q, const void* cache, void* out, 
     a.d = a.dv = 0; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
     a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
     a.pre_kind = 0; a.pre_n = 0; a.pool_slots = 0; a.page_extra = 0; a.vhead = -1;
+    a.vplanes = 0; a.out_plane = a.part_plane_rows = a.counters_plane = 0;
 }
 }  // namespace mhb_amma

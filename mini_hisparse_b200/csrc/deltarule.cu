@@ -5,15 +5,16 @@
 // with q, k, v from short causal convolutions over time (one filter per channel, then silu), q and k made unit
 // vectors per head, beta a sigmoid and g = exp(-exp(A_log) softplus(a + dt_bias)) one number per head and token.
 // Every column of S evolves on its own (column j sees v_t[j] only), so the recurrence is cut along the value
-// columns: a group of 8 lanes owns one column, each lane a slice of its dk rows in registers, and the two dot
-// products of a token are finished by three shuffles each.  Decoded tokens and prompt portions take the same
+// columns: a group of 4 lanes owns one column, each lane a run of dk / 4 rows in registers (the token's k and q
+// come as float4 from shared memory, the sums run in four chains), and the two dot products of a token are
+// finished by two shuffles each.  Decoded tokens and prompt portions take the same
 // kernel; a segment that starts at position 0 starts from zero, whatever its slot held.
 //
 //   delta_prep        per token: the convolutions of the q, k, v columns of the input projection (float32, possibly
 //                     split-K parts) over this step's rows and, before the segment's first row, the slot's last
 //                     taps - 1 inputs; silu; unit q (times dk^-1/2) and k; beta; g.  All float32.
 //   delta_conv_keep   per segment, after delta_prep: the last taps - 1 inputs of the segment go to its slot.
-//   delta_scan        the recurrence: one CTA per (segment, head, 16 value columns).
+//   delta_scan        the recurrence: one CTA of two warps per (segment, head, 16 value columns).
 #include "common.cuh"
 
 using namespace mhb;
@@ -22,8 +23,8 @@ MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
 
 namespace {
 constexpr int MAX_TAPS = 16;
-constexpr int LPC = 8;          // lanes per state column
-constexpr int COLS = 16;        // state columns per CTA (128 threads)
+constexpr int LPC = 4;          // lanes per state column
+constexpr int COLS = 16;        // state columns per CTA (64 threads)
 constexpr int TOK_CHUNK = 16;   // tokens whose inputs are staged at once
 
 struct Parts {
@@ -154,11 +155,12 @@ struct ScanArgs {
     int T, H, G, dk, dv, writable;
 };
 
-template <int RPL>       // rows of a column per lane: dk <= 8 RPL
+template <int RPL>       // rows of a column per lane: dk <= LPC * RPL; lane `sub` of a column owns the rows sub * RPL ...
 __global__ void __launch_bounds__(LPC * COLS)
 scan_kernel(const ScanArgs a) {
-    __shared__ float qs[TOK_CHUNK][LPC * RPL];
-    __shared__ float ks[TOK_CHUNK][LPC * RPL];
+    constexpr int RUN = RPL + 4;             // a lane's run of rows, padded so that the four lanes' float4 loads meet no bank twice
+    __shared__ __align__(16) float qs[TOK_CHUNK][LPC * RUN];
+    __shared__ __align__(16) float ks[TOK_CHUNK][LPC * RUN];
     __shared__ float vs[TOK_CHUNK][COLS];
     __shared__ float bs[TOK_CHUNK], gs[TOK_CHUNK];
     pdl_launch_dependents();
@@ -176,7 +178,7 @@ scan_kernel(const ScanArgs a) {
     float S[RPL];
 #pragma unroll
     for (int r = 0; r < RPL; ++r) {
-        const int i = sub + LPC * r;
+        const int i = sub * RPL + r;
         S[r] = (!fresh && live && i < dk) ? slot[(size_t)i * dv + j] : 0.f;
     }
     const int QK = a.G * dk, VW = a.H * dv;
@@ -186,8 +188,9 @@ scan_kernel(const ScanArgs a) {
         for (int idx = threadIdx.x; idx < n * LPC * RPL; idx += blockDim.x) {
             const int tt = idx / (LPC * RPL), i = idx - tt * (LPC * RPL);
             const size_t src = (size_t)(c0 + tt) * QK + hk * dk + i;
-            qs[tt][i] = i < dk ? a.q[src] : 0.f;
-            ks[tt][i] = i < dk ? a.k[src] : 0.f;
+            const int at = (i / RPL) * RUN + i % RPL;
+            qs[tt][at] = i < dk ? a.q[src] : 0.f;
+            ks[tt][at] = i < dk ? a.k[src] : 0.f;
         }
         for (int idx = threadIdx.x; idx < n * COLS; idx += blockDim.x) {
             const int tt = idx / COLS, c = idx - tt * COLS;
@@ -200,32 +203,50 @@ scan_kernel(const ScanArgs a) {
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
             const float g = gs[tt];
-            float dot = 0.f;
+            float kr[RPL];
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][sub * RUN]);
 #pragma unroll
-            for (int r = 0; r < RPL; ++r) {
-                S[r] *= g;
-                dot = fmaf(S[r], ks[tt][sub + LPC * r], dot);
+            for (int r = 0; r < RPL / 4; ++r) {
+                const float4 x = k4[r];
+                kr[4 * r] = x.x; kr[4 * r + 1] = x.y; kr[4 * r + 2] = x.z; kr[4 * r + 3] = x.w;
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;       // four chains, so that no product waits for the one before
+#pragma unroll
+            for (int r = 0; r < RPL; r += 4) {
+                S[r] *= g; S[r + 1] *= g; S[r + 2] *= g; S[r + 3] *= g;
+                d0 = fmaf(S[r], kr[r], d0);
+                d1 = fmaf(S[r + 1], kr[r + 1], d1);
+                d2 = fmaf(S[r + 2], kr[r + 2], d2);
+                d3 = fmaf(S[r + 3], kr[r + 3], d3);
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+            for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
             const float u = bs[tt] * (vs[tt][cl] - dot);
-            float o = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][sub * RUN]);
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < RPL; ++r) {
-                S[r] = fmaf(ks[tt][sub + LPC * r], u, S[r]);
-                o = fmaf(S[r], qs[tt][sub + LPC * r], o);
+            for (int r = 0; r < RPL / 4; ++r) {
+                const float4 x = q4[r];
+                S[4 * r] = fmaf(kr[4 * r], u, S[4 * r]);
+                S[4 * r + 1] = fmaf(kr[4 * r + 1], u, S[4 * r + 1]);
+                S[4 * r + 2] = fmaf(kr[4 * r + 2], u, S[4 * r + 2]);
+                S[4 * r + 3] = fmaf(kr[4 * r + 3], u, S[4 * r + 3]);
+                o0 = fmaf(S[4 * r], x.x, o0);
+                o1 = fmaf(S[4 * r + 1], x.y, o1);
+                o2 = fmaf(S[4 * r + 2], x.z, o2);
+                o3 = fmaf(S[4 * r + 3], x.w, o3);
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            float o = (o0 + o1) + (o2 + o3);
+#pragma unroll
+            for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (sub == 0 && live) a.out[(size_t)(c0 + tt) * VW + h * dv + j] = o;
         }
     }
     if (a.writable && live) {
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
-            const int i = sub + LPC * r;
+            const int i = sub * RPL + r;
             if (i < dk) slot[(size_t)i * dv + j] = S[r];
         }
     }
@@ -278,10 +299,11 @@ MHB_EXPORT int mhb_delta_scan(const float* q, const float* k, const float* v, co
     a.dk = dk; a.dv = dv; a.writable = writable;
     dim3 grid(S, H, (dv + COLS - 1) / COLS);
     cudaError_t e;
-    if (dk <= 32) e = launch_kernel(scan_kernel<4>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 64) e = launch_kernel(scan_kernel<8>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 128) e = launch_kernel(scan_kernel<16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else e = launch_kernel(scan_kernel<32>, grid, dim3(LPC * COLS), 0, stream, a);
+    if (dk <= 16) e = launch_kernel(scan_kernel<4>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 32) e = launch_kernel(scan_kernel<8>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 64) e = launch_kernel(scan_kernel<16>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 128) e = launch_kernel(scan_kernel<32>, grid, dim3(LPC * COLS), 0, stream, a);
+    else e = launch_kernel(scan_kernel<64>, grid, dim3(LPC * COLS), 0, stream, a);
     if (e != cudaSuccess) return fail("delta_scan: %s", cudaGetErrorString(e));
     return check_launch("delta_scan");
 }

@@ -564,8 +564,9 @@ def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
     all KV heads followed by their values, a ``sink`` per query head, a ``gate`` on the output; the softmax's
     weights enter the value product as two bfloat16 numbers each (16 bits instead of 8).  ``kparts``,
     ``softcap``, ``shared_kv``, ``gate_per_head``, ``keep_first`` and ``pool`` as in attention_simt; ``out`` may be
-    float32.  ``value_head``: every query head's weights are applied to the values of that one KV head (a mixer
-    that mixes the heads' weights calls once per KV head)."""
+    float32.  ``value_head``: every query head's weights are applied to the values of that one KV head; "all": to
+    the values of every KV head in turn in one launch, ``out`` being [nkv, T, nq, dv] (a plane per KV head), the partial
+    buffers [nkv, rows, nq, ...] and the counters [nkv, ...] likewise (for a mixer that mixes the heads' weights)."""
     lib = build.load("attention_mma_ext")
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or not cache.is_contiguous():
         raise KernelError("attention_mma_ext: q and the (contiguous) pool must be bfloat16")
@@ -579,13 +580,22 @@ def attention_mma_ext(q, cache, out, part_acc, part_ml, items, num_items, rows, 
             raise KernelError("attention: kept first positions or pooled blocks, not both")
         if kparts != 1 or softcap or shared_kv or gate_per_head or sink is not None:
             raise KernelError("attention: keys beyond the window go with plain keys and values only")
+        planes = (0, 0, 0)
+        if value_head == "all":
+            if tuple(out.shape[:1]) != (nkv,) or part_acc.shape[0] != nkv or part_ml.shape[0] != nkv or not out.is_contiguous():
+                raise KernelError("attention: with the values of every KV head the output and the partial buffers have a plane per KV head")
+            if counters is not None and counters.numel() % nkv:
+                raise KernelError("attention: the counters have a plane per KV head")
+            planes = (out[0].numel(), part_acc.shape[1], 0 if counters is None else counters.numel() // nkv)
+            value_head = -2
         _check(lib, lib.mhb_attention_mma_masked(
             _ptr(q), _ptr(cache), _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(items), c_int(num_items),
             c_int(num_items), c_int(rows), _ptr(positions), _ptr(block_table), c_int(block_table.shape[-1]),
             _ptr(tok_part_row), _ptr(tok_nsplit), _ptr(counters), c_int(nq), c_int(nkv), c_int(d), c_int(dv),
             c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), g[0], g[1], g[2], g[3],
             c_int(1 if out.dtype == torch.float32 else 0), c_int(1 if keep_first else 2 if pool else 0),
-            c_int(keep_first or pool or 0), c_int(-1 if value_head is None else value_head), _stream()),
+            c_int(keep_first or pool or 0), c_int(-1 if value_head is None else value_head),
+            *(c_longlong(x) for x in planes), _stream()),
             "attention_mma_ext")
         return
     _check(lib, lib.mhb_attention_mma_ext(

@@ -81,11 +81,13 @@ class WindowAttentionBase(Mixer):
         return proj, q
 
     def _attend_mma(self, q, out, ctx: StepContext, cache: CacheView, **options):
-        """The plan's items on the tensor cores: 16-row tiles whose key splits the last CTA merges, 64-row tiles."""
+        """The plan's items on the tensor cores: 16-row tiles whose key splits the last CTA merges, 64-row tiles.
+        With value_head="all" everything the kernel writes has a plane per KV head."""
         ws, meta, T = ctx.ws, cache.meta, q.shape[0]
         part_rows = max(1, meta["part_rows_cap"])
-        part_acc = ws.get("attn_part_acc", (part_rows, self.nq, self.dv), torch.float32)
-        part_ml = ws.get("attn_part_ml", (part_rows, self.nq, 2), torch.float32)
+        planes = (self.nkv,) if options.get("value_head") == "all" else ()
+        part_acc = ws.get("attn_part_acc", planes + (part_rows, self.nq, self.dv), torch.float32)
+        part_ml = ws.get("attn_part_ml", planes + (part_rows, self.nq, 2), torch.float32)
         n_small, n_big = meta["n_small"], meta["n_big"]
         args = (q, cache.storage, out, part_acc, part_ml)
         tail = (ctx.positions, meta["block_table"], meta["tok_part_row"])
@@ -93,7 +95,7 @@ class WindowAttentionBase(Mixer):
                       scale=self.scale, **options)
         if n_small:
             chunks = -(-(self.nq // self.nkv) // ROW_TILE)
-            counters = ws.get_zeroed("attn_counters", (T * self.nkv * chunks,), torch.int32)
+            counters = ws.get_zeroed("attn_counters", planes + (T * self.nkv * chunks,), torch.int32)
             K.attention_mma_ext(*args, meta["items"], n_small, 16, *tail, **common, tok_nsplit=meta["tok_nsplit"],
                                 counters=counters)
         if n_big:
@@ -226,10 +228,9 @@ class KeptFirstAttention(WindowAttentionBase):
         wide = self.nkv * self.dv
         attn = ws.get("wa_attn", (T, self.ow), rt.dtype)
         if self.kernel_family() == "mma":
-            # one pass per KV head: every query head's weights over that head's values, a plane of outputs each
+            # every query head's weights over the values of each KV head in turn (gridDim.z), a plane of outputs each
             planes = ws.get("wa_every", (self.nkv, T, self.nq, self.dv), torch.float32)
-            for c in range(self.nkv):
-                self._attend_mma(q, planes[c], ctx, cache, keep_first=self.keep_first, value_head=c)
+            self._attend_mma(q, planes, ctx, cache, keep_first=self.keep_first, value_head="all")
             K.talk_mix(planes, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv, planes=True)
         else:
             every = ws.get("wa_every", (T, self.nq, wide), torch.float32)

@@ -201,9 +201,10 @@ def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_
     T = sum(s.count for s in segments)
     plan = plan_attention(AttentionShape(nq, pool_.G, window, 64 if kernel == "mma" else 16), segments, T, sm_count=split_sms)
     n = plan.n_small + plan.n_big
-    part_acc = torch.empty(max(1, plan.part_rows), nq, out_width, device="cuda")
-    part_ml = torch.empty(max(1, plan.part_rows), nq, 2, device="cuda")
-    o = torch.zeros(T, nq, out_width, dtype=out_dtype, device="cuda")
+    planes = (pool_.G,) if opts.get("value_head") == "all" else ()
+    part_acc = torch.empty(*planes, max(1, plan.part_rows), nq, out_width, device="cuda")
+    part_ml = torch.empty(*planes, max(1, plan.part_rows), nq, 2, device="cuda")
+    o = torch.zeros(*planes, T, nq, out_width, dtype=out_dtype, device="cuda")
     tables = dev_i(pool_.table[None, :].repeat(len(segments), 1))
     positions = dev_i(torch.cat([torch.arange(s.start, s.start + s.count) for s in segments]))
     tpr, tns = dev_i(torch.from_numpy(plan.tok_part_row)), dev_i(torch.from_numpy(plan.tok_nsplit))
@@ -211,7 +212,7 @@ def run_attention(pool_, q_rows, segments, *, nq, window, scale, out_width, out_
         items = dev_i(torch.from_numpy(plan.items)).view(-1)
         common = dict(nq=nq, nkv=pool_.G, d=pool_.d, dv=pool_.dv, page_size=pool_.P, window=window, scale=scale, **opts)
         if plan.n_small:
-            counters = torch.zeros(T * pool_.G * -(-(nq // pool_.G) // 16), dtype=torch.int32, device="cuda")
+            counters = torch.zeros(*planes, T * pool_.G * -(-(nq // pool_.G) // 16), dtype=torch.int32, device="cuda")
             K.attention_mma_ext(q_rows, pool_.storage, o, part_acc, part_ml, items, plan.n_small, 16, positions, tables,
                                 tpr, **common, tok_nsplit=tns, counters=counters)
             assert int(counters.abs().sum()) == 0
@@ -411,11 +412,15 @@ def test_window_with_kept_first_positions_and_mixed_heads(H, G, d, dv, P_, size,
         ref = P.kept_first_mixed(qd.cpu().double(), kc, vc, talk.double(), scale, size, keep, qpos=qpos)
         for sms in (148, 100000):
             out = torch.empty(T, H * dv, dtype=dtype, device="cuda")
-            if kernel == "mma":       # one pass per KV head, a plane of outputs each
+            if kernel == "mma":       # the values of one KV head a launch, and of every KV head in one launch: a plane each
                 planes = [run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=dv,
                                         out_dtype=torch.float32, split_sms=sms, kernel="mma", keep_first=keep,
                                         value_head=c)[0] for c in range(G)]
-                K.talk_mix(torch.stack(planes).float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv, planes=True)
+                both, _ = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=dv,
+                                        out_dtype=torch.float32, split_sms=sms, kernel="mma", keep_first=keep,
+                                        value_head="all")
+                assert torch.equal(both, torch.stack(planes))
+                K.talk_mix(both.float().cuda().contiguous(), talk.cuda(), out, nq=H, nkv=G, dv=dv, planes=True)
             else:
                 wide, plan = run_attention(pl, qd.view(T, H * d), segs, nq=H, window=size, scale=scale, out_width=G * dv,
                                            out_dtype=torch.float32, split_sms=sms, keep_first=keep, all_values=True)
