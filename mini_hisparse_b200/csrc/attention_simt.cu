@@ -77,6 +77,7 @@ struct AttnArgs {
     int pre_kind, pre_n;       // keys seen beyond the window: 0 none, 1 the first pre_n positions, 2 means of blocks of pre_n
     int pool_slots;            // pooled rows per page and KV head (pre_kind 2)
     int vheads;                // 1, or nkv: values of every KV head
+    int vhead;                 // >= 0 (with vheads 1): the values of this KV head, whatever the query head's own
     size_t page_extra;         // elements of a page behind its keys and values
 };
 
@@ -176,7 +177,7 @@ attention_simt_kernel(const AttnArgs a) {
                     const size_t off = pbase + kv_elems + ((size_t)kvh * a.pool_slots + slot) * d;
                     for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
                     for (int c = 0; c < a.vheads; ++c) {
-                        const int vh = a.vheads > 1 ? c : kvh;
+                        const int vh = a.vheads > 1 ? c : (a.vhead >= 0 ? a.vhead : kvh);
                         const size_t voff = pbase + kv_elems + (size_t)a.nkv * a.pool_slots * d +
                                             ((size_t)vh * a.pool_slots + slot) * dv1;
                         for (int e = lane; e < dv1; e += 32) v_s[j * dv + c * dv1 + e] = to_float(cache[voff + e]);
@@ -185,7 +186,7 @@ attention_simt_kernel(const AttnArgs a) {
                     const size_t off = pbase + ((size_t)kvh * a.P + slot) * k_ld + map * d;
                     for (int e = lane; e < d; e += 32) k_s[j * (d + 1) + e] = to_float(cache[off + e]);
                     for (int c = 0; c < a.vheads; ++c) {
-                        const int vh = a.vheads > 1 ? c : kvh;
+                        const int vh = a.vheads > 1 ? c : (a.vhead >= 0 ? a.vhead : kvh);
                         const size_t voff = pbase + v_plane + ((size_t)vh * a.P + slot) * v_ld;
                         for (int e = lane; e < dv1; e += 32) v_s[j * dv + c * dv1 + e] = to_float(cache[voff + e]);
                     }
@@ -357,7 +358,7 @@ MHB_EXPORT int mhb_attention_simt(const void* q, const void* cache, void* out, i
     a.nkv = nkv; a.d = d; a.P = P; a.num_pages = num_pages; a.window = window; a.scale = scale;
     a.dv = d; a.sink = nullptr; a.gate = nullptr; a.gate_nsplit = 1; a.gate_ld = 0; a.gate_split_stride = 0;
     a.kparts = 1; a.softcap = 0.f; a.shared_kv = 0; a.gate_per_head = 0; a.out_f32 = 0;
-    a.pre_kind = 0; a.pre_n = 0; a.pool_slots = 0; a.vheads = 1; a.page_extra = 0;
+    a.pre_kind = 0; a.pre_n = 0; a.pool_slots = 0; a.vheads = 1; a.page_extra = 0; a.vhead = -1;
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
     return 0;
 }
@@ -390,7 +391,9 @@ int attention_simt_options(const void* q, const void* cache, void* out, int dtyp
     a.gate_split_stride = (size_t)gate_split_stride;
     a.kparts = kparts; a.softcap = softcap; a.shared_kv = shared_kv; a.gate_per_head = gate_per_head;
     a.out_f32 = out_f32;
-    a.pre_kind = pre_kind; a.pre_n = pre_n; a.vheads = all_values ? nkv : 1;
+    a.pre_kind = pre_kind; a.pre_n = pre_n; a.vheads = all_values == 1 ? nkv : 1;
+    a.vhead = all_values >= 2 ? all_values - 2 : -1;          // 2 + c: the values of KV head c alone
+    if (a.vhead >= nkv) return fail("attention: values of KV head %d of %d", a.vhead, nkv);
     a.pool_slots = pre_kind == 2 ? (P + pre_n - 1) / pre_n : 0;
     a.page_extra = (size_t)nkv * a.pool_slots * (d + dv);
     MHB_DISPATCH_DTYPE(dtype, CT, return launch_attention<CT>(a, max_items, stream));
@@ -413,7 +416,8 @@ MHB_EXPORT int mhb_attention_simt_ext(const void* q, const void* cache, void* ou
 }
 
 // The same with keys that stay visible beyond the window (pre_kind, pre_n) and with the values of every KV head
-// under each query head's weights (all_values): see "prefix" and "vheads" at the top.
+// under each query head's weights (all_values 1; 2 + c: the values of KV head c alone, for rows too wide to hold all):
+// see "prefix" and "vheads" at the top.
 MHB_EXPORT int mhb_attention_simt_masked(const void* q, const void* cache, void* out, int dtype,
                                          float* part_acc, float* part_ml, const int* items, int num_items,
                                          int max_items, const int* positions, const int* block_table,

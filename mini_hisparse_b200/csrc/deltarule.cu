@@ -6,8 +6,8 @@
 // vectors per head, beta a sigmoid and g = exp(-exp(A_log) softplus(a + dt_bias)) one number per head and token.
 // Every column of S evolves on its own (column j sees v_t[j] only), so the recurrence is cut along the value
 // columns: a group of 4 lanes owns one column, each lane a run of dk / 4 rows in registers (the token's k and q
-// come as float4 from shared memory, the sums run in four chains), and the two dot products of a token are
-// finished by two shuffles each.  Decoded tokens and prompt portions take the same
+// come as float4 from shared memory, where cp.async put them while the 16 tokens before were walked; the sums run
+// in four chains), and the two dot products of a token are finished by two shuffles each.  Decoded tokens and prompt portions take the same
 // kernel; a segment that starts at position 0 starts from zero, whatever its slot held.
 //
 //   delta_prep        per token: the convolutions of the q, k, v columns of the input projection (float32, possibly
@@ -25,7 +25,6 @@ namespace {
 constexpr int MAX_TAPS = 16;
 constexpr int LPC = 4;          // lanes per state column
 constexpr int COLS = 16;        // state columns per CTA (64 threads)
-constexpr int TOK_CHUNK = 16;   // tokens whose inputs are staged at once
 
 struct Parts {
     const float* p;
@@ -155,14 +154,25 @@ struct ScanArgs {
     int T, H, G, dk, dv, writable;
 };
 
-template <int RPL>       // rows of a column per lane: dk <= LPC * RPL; lane `sub` of a column owns the rows sub * RPL ...
+__device__ __forceinline__ void copy_async4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// RPL: rows of a column per lane (dk <= LPC * RPL; lane `sub` of a column owns the rows sub * RPL ...).  CH: tokens whose
+// inputs are staged at once; the next CH tokens' inputs arrive by cp.async while these are walked.
+template <int RPL, int CH>
 __global__ void __launch_bounds__(LPC * COLS)
 scan_kernel(const ScanArgs a) {
     constexpr int RUN = RPL + 4;             // a lane's run of rows, padded so that the four lanes' float4 loads meet no bank twice
-    __shared__ __align__(16) float qs[TOK_CHUNK][LPC * RUN];
-    __shared__ __align__(16) float ks[TOK_CHUNK][LPC * RUN];
-    __shared__ float vs[TOK_CHUNK][COLS];
-    __shared__ float bs[TOK_CHUNK], gs[TOK_CHUNK];
+    __shared__ __align__(16) float qs[2][CH][LPC * RUN];
+    __shared__ __align__(16) float ks[2][CH][LPC * RUN];
+    __shared__ float vs[2][CH][COLS];
+    __shared__ float bs[2][CH], gs[2][CH];
     pdl_launch_dependents();
     pdl_wait();
     const int seg = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * COLS;
@@ -173,6 +183,44 @@ scan_kernel(const ScanArgs a) {
     const int sub = threadIdx.x % LPC, cl = threadIdx.x / LPC;
     const int j = col0 + cl;
     const bool live = j < dv;
+    const int QK = a.G * dk, VW = a.H * dv;
+    // what no copy ever writes (rows beyond dk, columns beyond dv) stays zero
+    for (int i = threadIdx.x; i < 2 * CH * LPC * RUN; i += blockDim.x) { (&qs[0][0][0])[i] = 0.f; (&ks[0][0][0])[i] = 0.f; }
+    for (int i = threadIdx.x; i < 2 * CH * COLS; i += blockDim.x) (&vs[0][0][0])[i] = 0.f;
+    __syncthreads();
+    const bool by4 = dk % 4 == 0 && ((uintptr_t)a.q & 15) == 0 && ((uintptr_t)a.k & 15) == 0;     // rows then start on 16 bytes
+    auto stage_in = [&](int st, int c0) {
+        const int n = min(CH, t1 - c0);
+        if (by4) {
+            const int per = dk / 4;
+            for (int idx = threadIdx.x; idx < n * per; idx += blockDim.x) {
+                const int tt = idx / per, i = (idx - tt * per) * 4;
+                const size_t src = (size_t)(c0 + tt) * QK + hk * dk + i;
+                const int at = (i / RPL) * RUN + i % RPL;
+                copy_async16(&qs[st][tt][at], a.q + src);
+                copy_async16(&ks[st][tt][at], a.k + src);
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
+                const int tt = idx / dk, i = idx - tt * dk;
+                const size_t src = (size_t)(c0 + tt) * QK + hk * dk + i;
+                const int at = (i / RPL) * RUN + i % RPL;
+                copy_async4(&qs[st][tt][at], a.q + src);
+                copy_async4(&ks[st][tt][at], a.k + src);
+            }
+        }
+        const int cols = min(COLS, dv - col0);
+        for (int idx = threadIdx.x; idx < n * cols; idx += blockDim.x) {
+            const int tt = idx / cols, c = idx - tt * cols;
+            copy_async4(&vs[st][tt][c], a.v + (size_t)(c0 + tt) * VW + h * dv + col0 + c);
+        }
+        if (threadIdx.x < n) {
+            copy_async4(&bs[st][threadIdx.x], a.beta + (size_t)(c0 + threadIdx.x) * a.H + h);
+            copy_async4(&gs[st][threadIdx.x], a.decay + (size_t)(c0 + threadIdx.x) * a.H + h);
+        }
+    };
+    stage_in(0, t0);
+    copy_async_commit();
     float* slot = a.state + (size_t)a.seg_slot[seg] * a.state_stride + (size_t)h * dk * dv;
     const bool fresh = a.positions[t0] == 0;
     float S[RPL];
@@ -181,30 +229,17 @@ scan_kernel(const ScanArgs a) {
         const int i = sub * RPL + r;
         S[r] = (!fresh && live && i < dk) ? slot[(size_t)i * dv + j] : 0.f;
     }
-    const int QK = a.G * dk, VW = a.H * dv;
-    for (int c0 = t0; c0 < t1; c0 += TOK_CHUNK) {
-        const int n = min(TOK_CHUNK, t1 - c0);
-        __syncthreads();
-        for (int idx = threadIdx.x; idx < n * LPC * RPL; idx += blockDim.x) {
-            const int tt = idx / (LPC * RPL), i = idx - tt * (LPC * RPL);
-            const size_t src = (size_t)(c0 + tt) * QK + hk * dk + i;
-            const int at = (i / RPL) * RUN + i % RPL;
-            qs[tt][at] = i < dk ? a.q[src] : 0.f;
-            ks[tt][at] = i < dk ? a.k[src] : 0.f;
-        }
-        for (int idx = threadIdx.x; idx < n * COLS; idx += blockDim.x) {
-            const int tt = idx / COLS, c = idx - tt * COLS;
-            vs[tt][c] = col0 + c < dv ? a.v[(size_t)(c0 + tt) * VW + h * dv + col0 + c] : 0.f;
-        }
-        if (threadIdx.x < n) {
-            bs[threadIdx.x] = a.beta[(size_t)(c0 + threadIdx.x) * a.H + h];
-            gs[threadIdx.x] = a.decay[(size_t)(c0 + threadIdx.x) * a.H + h];
-        }
+    int st = 0;
+    for (int c0 = t0; c0 < t1; c0 += CH, st ^= 1) {
+        const int n = min(CH, t1 - c0);
+        if (c0 + CH < t1) stage_in(st ^ 1, c0 + CH);
+        copy_async_commit();
+        copy_async_wait<1>();          // everything but the copies just issued has landed
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
-            const float g = gs[tt];
+            const float g = gs[st][tt];
             float kr[RPL];
-            const float4* k4 = reinterpret_cast<const float4*>(&ks[tt][sub * RUN]);
+            const float4* k4 = reinterpret_cast<const float4*>(&ks[st][tt][sub * RUN]);
 #pragma unroll
             for (int r = 0; r < RPL / 4; ++r) {
                 const float4 x = k4[r];
@@ -222,8 +257,8 @@ scan_kernel(const ScanArgs a) {
             float dot = (d0 + d1) + (d2 + d3);
 #pragma unroll
             for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = bs[tt] * (vs[tt][cl] - dot);
-            const float4* q4 = reinterpret_cast<const float4*>(&qs[tt][sub * RUN]);
+            const float u = bs[st][tt] * (vs[st][tt][cl] - dot);
+            const float4* q4 = reinterpret_cast<const float4*>(&qs[st][tt][sub * RUN]);
             float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int r = 0; r < RPL / 4; ++r) {
@@ -242,7 +277,9 @@ scan_kernel(const ScanArgs a) {
             for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
             if (sub == 0 && live) a.out[(size_t)(c0 + tt) * VW + h * dv + j] = o;
         }
+        __syncthreads();               // this stage is free for the copies of the chunk after the next
     }
+    copy_async_wait<0>();
     if (a.writable && live) {
 #pragma unroll
         for (int r = 0; r < RPL; ++r) {
@@ -299,11 +336,11 @@ MHB_EXPORT int mhb_delta_scan(const float* q, const float* k, const float* v, co
     a.dk = dk; a.dv = dv; a.writable = writable;
     dim3 grid(S, H, (dv + COLS - 1) / COLS);
     cudaError_t e;
-    if (dk <= 16) e = launch_kernel(scan_kernel<4>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 32) e = launch_kernel(scan_kernel<8>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 64) e = launch_kernel(scan_kernel<16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 128) e = launch_kernel(scan_kernel<32>, grid, dim3(LPC * COLS), 0, stream, a);
-    else e = launch_kernel(scan_kernel<64>, grid, dim3(LPC * COLS), 0, stream, a);
+    if (dk <= 16) e = launch_kernel(scan_kernel<4, 16>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 32) e = launch_kernel(scan_kernel<8, 16>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 64) e = launch_kernel(scan_kernel<16, 16>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 128) e = launch_kernel(scan_kernel<32, 16>, grid, dim3(LPC * COLS), 0, stream, a);
+    else e = launch_kernel(scan_kernel<64, 8>, grid, dim3(LPC * COLS), 0, stream, a);
     if (e != cudaSuccess) return fail("delta_scan: %s", cudaGetErrorString(e));
     return check_launch("delta_scan");
 }

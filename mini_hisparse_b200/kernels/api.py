@@ -454,7 +454,7 @@ def gemm_tc_qkv_rope(x, w, bias, cos_sin, positions, tok_seg, block_table, q_out
 def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items, positions,
                    block_table, tok_part_row, *, nq, nkv, d, page_size, window=0, scale=None, dv=None,
                    sink=None, gate=None, gate_nsplit=1, gate_split_stride=0, kparts=1, softcap=0.0,
-                   shared_kv=False, gate_per_head=False, keep_first=0, pool=0, all_values=False):
+                   shared_kv=False, gate_per_head=False, keep_first=0, pool=0, all_values=False, value_head=None):
     """CUDA-core attention over the items of a plan.  Options: ``dv`` values of another width than the
     keys (a page then holds the keys of all KV heads followed by their values), ``sink`` float32 [nq]
     (one extra term exp(sink_h) in the softmax's denominator), ``gate`` (the output is multiplied by its
@@ -465,11 +465,11 @@ def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items
     start of a sequence stay visible, or (``pool``) every block of ``pool`` positions that the window has passed
     wholly is seen as one key and value, its means, from the tail of its page (csrc/maskparts.cu).
     ``all_values``: every query head's weights are applied to the values of all KV heads, and ``out`` is
-    [T, nq, nkv * dv]."""
+    [T, nq, nkv * dv]; ``value_head``: to the values of that one KV head."""
     lib = build.load("attention_simt")
     if scale is None:
         scale = float(d) ** -0.5
-    if keep_first or pool or all_values:
+    if keep_first or pool or all_values or value_head is not None:
         if keep_first and pool:
             raise KernelError("attention: kept first positions or pooled blocks, not both")
         if kparts != 1 or softcap or shared_kv or gate_per_head:
@@ -482,7 +482,7 @@ def attention_simt(q, cache, out, part_acc, part_ml, items, num_items, max_items
             c_int(page_size), c_int(cache.shape[0]), c_int(window or 0), c_float(scale), _ptr(sink),
             g[0], g[1], g[2], g[3], c_int(1 if out.dtype == torch.float32 else 0),
             c_int(1 if keep_first else 2 if pool else 0), c_int(keep_first or pool or 0),
-            c_int(1 if all_values else 0), _stream()), "attention")
+            c_int(1 if all_values else 0 if value_head is None else 2 + value_head), _stream()), "attention")
         return
     general = kparts != 1 or softcap or shared_kv or gate_per_head or out.dtype != q.dtype
     if dv is not None or sink is not None or gate is not None or general:

@@ -48,6 +48,8 @@ class WindowAttentionBase(Mixer):
         (bfloat16, widths that are multiples of 8 up to 128); "simt": the CUDA cores (float32, and every other width)."""
         if self.rt is None or self.rt.dtype != torch.bfloat16 or not K.attention_mma_ext_supports(self.dk, self.dv):
             return "simt"
+        if not self.scale > 0.0:        # the tensor-core kernels take the running maximum of the raw products
+            return "simt"
         return "mma"
 
     def kernel_modules(self):
@@ -197,9 +199,8 @@ class KeptFirstAttention(WindowAttentionBase):
         self.keep_first = int(spec["keep_first"])
         if self.keep_first < 0:
             raise ValueError("keep_first cannot be negative")
-        if self.kernel_family() == "simt" and self.nkv * self.dv > 512:
-            raise ValueError(f"values of {self.nkv} KV heads x {self.dv}: the CUDA-core kernel that applies every head's "
-                             "weights to all of them takes up to 512")
+        if self.dv > 512:
+            raise ValueError(f"values {self.dv} wide: the attention kernels take up to 512")
         self.talk = None
 
     def cache_need(self):
@@ -232,8 +233,13 @@ class KeptFirstAttention(WindowAttentionBase):
             planes = ws.get("wa_every", (self.nkv, T, self.nq, self.dv), torch.float32)
             self._attend_mma(q, planes, ctx, cache, keep_first=self.keep_first, value_head="all")
             K.talk_mix(planes, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv, planes=True)
-        else:
+        elif wide <= 512:
             every = ws.get("wa_every", (T, self.nq, wide), torch.float32)
             self._attend(q, every, wide, ctx, cache, keep_first=self.keep_first, all_values=True)
             K.talk_mix(every, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv)
+        else:       # rows too wide for one pass on the CUDA cores: a pass and a plane per KV head
+            planes = ws.get("wa_every", (self.nkv, T, self.nq, self.dv), torch.float32)
+            for c in range(self.nkv):
+                self._attend(q, planes[c], self.dv, ctx, cache, keep_first=self.keep_first, value_head=c)
+            K.talk_mix(planes, self.talk, attn, nq=self.nq, nkv=self.nkv, dv=self.dv, planes=True)
         return rt.linear(attn, self.o_weight, ws, "mix_out", out_dtype=torch.float32)

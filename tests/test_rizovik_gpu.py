@@ -637,6 +637,23 @@ def test_far_tokens_reach_the_last_logits(tmp_path, dtype):
         check_rows(row_errors(got["r0"], whole["r0"]), dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_mixed_heads_over_values_too_wide_for_one_pass(tmp_path, dtype):
+    """Five KV heads with values 112 wide: 560 numbers a row, more than one pass of the CUDA-core kernel holds, so it
+    goes once per KV head (float32); on the tensor cores every KV head is a plane of one launch (bfloat16)."""
+    from mini_hisparse_b200 import write_random_model
+
+    cfg = model(90, 64, [layer("attention_2", kept(5, 5, 16, 112, 12, 2, rot=8), moe(3, 1, 16)),
+                         layer("attention_2", kept(10, 5, 16, 112, 9, 0), None)], mult=0.8)
+    write_random_model(cfg, 13, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
+    cfg, w = P.load_folder(tmp_path)
+    reqs = requests_for(cfg, [70, 19], seed=20)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    for steps in (S.whole(reqs), S.changing_portions(reqs, sizes=(20, 2, 7, 1, 1, 3))):
+        got, stats, pages = run_steps(tmp_path, dtype, steps)
+        check_against_plain(got, refs, dtype)
+
+
 def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
     """A window one key off, a block size or a kept count one off, unscaled frequencies, heads that are not mixed, a
     multiplier, a filter's tap, a layer that runs its own tensors instead of another's: each moves the plain model's
