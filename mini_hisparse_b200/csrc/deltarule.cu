@@ -14,7 +14,7 @@
 //                     split-K parts) over this step's rows and, before the segment's first row, the slot's last
 //                     taps - 1 inputs; silu; unit q (times dk^-1/2) and k; beta; g.  All float32.
 //   delta_conv_keep   per segment, after delta_prep: the last taps - 1 inputs of the segment go to its slot.
-//   delta_scan        the recurrence: one CTA of two warps per (segment, head, 16 value columns).
+//   delta_scan        the recurrence: one warp per (segment, head, 16 value columns), two columns a thread.
 #include "common.cuh"
 
 using namespace mhb;
@@ -24,7 +24,7 @@ MHB_EXPORT const char* mhb_last_error() { return error_buffer(); }
 namespace {
 constexpr int MAX_TAPS = 16;
 constexpr int LPC = 4;          // lanes per state column
-constexpr int COLS = 16;        // state columns per CTA (64 threads)
+constexpr int COLS = 16;        // state columns per CTA
 
 struct Parts {
     const float* p;
@@ -165,8 +165,9 @@ template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatil
 
 // RPL: rows of a column per lane (dk <= LPC * RPL; lane `sub` of a column owns the rows sub * RPL ...).  CH: tokens whose
 // inputs are staged at once; the next CH tokens' inputs arrive by cp.async while these are walked.
-template <int RPL, int CH>
-__global__ void __launch_bounds__(LPC * COLS)
+// CPT: columns per thread (two recurrences whose chains fill each other's waits, where the registers hold both).
+template <int RPL, int CH, int CPT>
+__global__ void __launch_bounds__(LPC * COLS / CPT)
 scan_kernel(const ScanArgs a) {
     constexpr int RUN = RPL + 4;             // a lane's run of rows, padded so that the four lanes' float4 loads meet no bank twice
     __shared__ __align__(16) float qs[2][CH][LPC * RUN];
@@ -181,8 +182,12 @@ scan_kernel(const ScanArgs a) {
     const int dk = a.dk, dv = a.dv;
     const int hk = h / (a.H / a.G);
     const int sub = threadIdx.x % LPC, cl = threadIdx.x / LPC;
-    const int j = col0 + cl;
-    const bool live = j < dv;
+    int cols_here[CPT];                                        // a thread's columns inside the CTA's 16
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) cols_here[c] = cl + c * (COLS / CPT);
+    bool live[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) live[c] = col0 + cols_here[c] < dv;
     const int QK = a.G * dk, VW = a.H * dv;
     // what no copy ever writes (rows beyond dk, columns beyond dv) stays zero
     for (int i = threadIdx.x; i < 2 * CH * LPC * RUN; i += blockDim.x) { (&qs[0][0][0])[i] = 0.f; (&ks[0][0][0])[i] = 0.f; }
@@ -223,12 +228,14 @@ scan_kernel(const ScanArgs a) {
     copy_async_commit();
     float* slot = a.state + (size_t)a.seg_slot[seg] * a.state_stride + (size_t)h * dk * dv;
     const bool fresh = a.positions[t0] == 0;
-    float S[RPL];
+    float S[CPT][RPL];
 #pragma unroll
-    for (int r = 0; r < RPL; ++r) {
-        const int i = sub * RPL + r;
-        S[r] = (!fresh && live && i < dk) ? slot[(size_t)i * dv + j] : 0.f;
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int r = 0; r < RPL; ++r) {
+            const int i = sub * RPL + r;
+            S[c][r] = (!fresh && live[c] && i < dk) ? slot[(size_t)i * dv + col0 + cols_here[c]] : 0.f;
+        }
     int st = 0;
     for (int c0 = t0; c0 < t1; c0 += CH, st ^= 1) {
         const int n = min(CH, t1 - c0);
@@ -245,47 +252,59 @@ scan_kernel(const ScanArgs a) {
                 const float4 x = k4[r];
                 kr[4 * r] = x.x; kr[4 * r + 1] = x.y; kr[4 * r + 2] = x.z; kr[4 * r + 3] = x.w;
             }
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;       // four chains, so that no product waits for the one before
+            float d[CPT][4];           // four chains a column, so that no product waits for the one before
 #pragma unroll
-            for (int r = 0; r < RPL; r += 4) {
-                S[r] *= g; S[r + 1] *= g; S[r + 2] *= g; S[r + 3] *= g;
-                d0 = fmaf(S[r], kr[r], d0);
-                d1 = fmaf(S[r + 1], kr[r + 1], d1);
-                d2 = fmaf(S[r + 2], kr[r + 2], d2);
-                d3 = fmaf(S[r + 3], kr[r + 3], d3);
+            for (int c = 0; c < CPT; ++c) d[c][0] = d[c][1] = d[c][2] = d[c][3] = 0.f;
+#pragma unroll
+            for (int r = 0; r < RPL; r += 4)
+#pragma unroll
+                for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        S[c][r + x] *= g;
+                        d[c][x] = fmaf(S[c][r + x], kr[r + x], d[c][x]);
+                    }
+            float u[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float dot = (d[c][0] + d[c][1]) + (d[c][2] + d[c][3]);
+#pragma unroll
+                for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                u[c] = bs[st][tt] * (vs[st][tt][cols_here[c]] - dot);
+                d[c][0] = d[c][1] = d[c][2] = d[c][3] = 0.f;
             }
-            float dot = (d0 + d1) + (d2 + d3);
-#pragma unroll
-            for (int o = 1; o < LPC; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-            const float u = bs[st][tt] * (vs[st][tt][cl] - dot);
             const float4* q4 = reinterpret_cast<const float4*>(&qs[st][tt][sub * RUN]);
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
             for (int r = 0; r < RPL / 4; ++r) {
-                const float4 x = q4[r];
-                S[4 * r] = fmaf(kr[4 * r], u, S[4 * r]);
-                S[4 * r + 1] = fmaf(kr[4 * r + 1], u, S[4 * r + 1]);
-                S[4 * r + 2] = fmaf(kr[4 * r + 2], u, S[4 * r + 2]);
-                S[4 * r + 3] = fmaf(kr[4 * r + 3], u, S[4 * r + 3]);
-                o0 = fmaf(S[4 * r], x.x, o0);
-                o1 = fmaf(S[4 * r + 1], x.y, o1);
-                o2 = fmaf(S[4 * r + 2], x.z, o2);
-                o3 = fmaf(S[4 * r + 3], x.w, o3);
-            }
-            float o = (o0 + o1) + (o2 + o3);
+                const float4 x4 = q4[r];
+                const float qv[4] = {x4.x, x4.y, x4.z, x4.w};
 #pragma unroll
-            for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
-            if (sub == 0 && live) a.out[(size_t)(c0 + tt) * VW + h * dv + j] = o;
+                for (int c = 0; c < CPT; ++c)
+#pragma unroll
+                    for (int x = 0; x < 4; ++x) {
+                        S[c][4 * r + x] = fmaf(kr[4 * r + x], u[c], S[c][4 * r + x]);
+                        d[c][x] = fmaf(S[c][4 * r + x], qv[x], d[c][x]);
+                    }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float o = (d[c][0] + d[c][1]) + (d[c][2] + d[c][3]);
+#pragma unroll
+                for (int x = 1; x < LPC; x <<= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+                if (sub == 0 && live[c]) a.out[(size_t)(c0 + tt) * VW + h * dv + col0 + cols_here[c]] = o;
+            }
         }
         __syncthreads();               // this stage is free for the copies of the chunk after the next
     }
     copy_async_wait<0>();
-    if (a.writable && live) {
+    if (a.writable) {
 #pragma unroll
-        for (int r = 0; r < RPL; ++r) {
-            const int i = sub * RPL + r;
-            if (i < dk) slot[(size_t)i * dv + j] = S[r];
-        }
+        for (int c = 0; c < CPT; ++c)
+#pragma unroll
+            for (int r = 0; r < RPL; ++r) {
+                const int i = sub * RPL + r;
+                if (live[c] && i < dk) slot[(size_t)i * dv + col0 + cols_here[c]] = S[c][r];
+            }
     }
 }
 }  // namespace
@@ -336,11 +355,11 @@ MHB_EXPORT int mhb_delta_scan(const float* q, const float* k, const float* v, co
     a.dk = dk; a.dv = dv; a.writable = writable;
     dim3 grid(S, H, (dv + COLS - 1) / COLS);
     cudaError_t e;
-    if (dk <= 16) e = launch_kernel(scan_kernel<4, 16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 32) e = launch_kernel(scan_kernel<8, 16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 64) e = launch_kernel(scan_kernel<16, 16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else if (dk <= 128) e = launch_kernel(scan_kernel<32, 16>, grid, dim3(LPC * COLS), 0, stream, a);
-    else e = launch_kernel(scan_kernel<64, 8>, grid, dim3(LPC * COLS), 0, stream, a);
+    if (dk <= 16) e = launch_kernel(scan_kernel<4, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
+    else if (dk <= 32) e = launch_kernel(scan_kernel<8, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
+    else if (dk <= 64) e = launch_kernel(scan_kernel<16, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
+    else if (dk <= 128) e = launch_kernel(scan_kernel<32, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
+    else e = launch_kernel(scan_kernel<64, 8, 1>, grid, dim3(LPC * COLS), 0, stream, a);
     if (e != cudaSuccess) return fail("delta_scan: %s", cudaGetErrorString(e));
     return check_launch("delta_scan");
 }
