@@ -14,7 +14,7 @@
 //                     split-K parts) over this step's rows and, before the segment's first row, the slot's last
 //                     taps - 1 inputs; silu; unit q (times dk^-1/2) and k; beta; g.  All float32.
 //   delta_conv_keep   per segment, after delta_prep: the last taps - 1 inputs of the segment go to its slot.
-//   delta_scan        the recurrence: one warp per (segment, head, 16 value columns), two columns a thread.
+//   delta_scan        the recurrence: one CTA of two warps per (segment, head, 16 value columns).
 #include "common.cuh"
 
 using namespace mhb;
@@ -165,7 +165,7 @@ template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatil
 
 // RPL: rows of a column per lane (dk <= LPC * RPL; lane `sub` of a column owns the rows sub * RPL ...).  CH: tokens whose
 // inputs are staged at once; the next CH tokens' inputs arrive by cp.async while these are walked.
-// CPT: columns per thread (two recurrences whose chains fill each other's waits, where the registers hold both).
+// CPT: columns per thread (two recurrences whose chains fill each other's waits; see the launch for why it is 1).
 template <int RPL, int CH, int CPT>
 __global__ void __launch_bounds__(LPC * COLS / CPT)
 scan_kernel(const ScanArgs a) {
@@ -355,10 +355,13 @@ MHB_EXPORT int mhb_delta_scan(const float* q, const float* k, const float* v, co
     a.dk = dk; a.dv = dv; a.writable = writable;
     dim3 grid(S, H, (dv + COLS - 1) / COLS);
     cudaError_t e;
-    if (dk <= 16) e = launch_kernel(scan_kernel<4, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
-    else if (dk <= 32) e = launch_kernel(scan_kernel<8, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
-    else if (dk <= 64) e = launch_kernel(scan_kernel<16, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
-    else if (dk <= 128) e = launch_kernel(scan_kernel<32, 16, 2>, grid, dim3(LPC * COLS / 2), 0, stream, a);
+    // One column a thread: with two (CPT = 2) a warp's chains do fill each other's waits (1.3 times the work a cycle),
+    // but a prompt of one request then has half as many warps, and they are what fills the GPU: 16 heads x 128 columns
+    // took 850 us with two columns a thread and 560 us with one.
+    if (dk <= 16) e = launch_kernel(scan_kernel<4, 16, 1>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 32) e = launch_kernel(scan_kernel<8, 16, 1>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 64) e = launch_kernel(scan_kernel<16, 16, 1>, grid, dim3(LPC * COLS), 0, stream, a);
+    else if (dk <= 128) e = launch_kernel(scan_kernel<32, 16, 1>, grid, dim3(LPC * COLS), 0, stream, a);
     else e = launch_kernel(scan_kernel<64, 8, 1>, grid, dim3(LPC * COLS), 0, stream, a);
     if (e != cudaSuccess) return fail("delta_scan: %s", cudaGetErrorString(e));
     return check_launch("delta_scan");
