@@ -60,6 +60,16 @@ def test_run_order_names_and_cache_needs():
     assert spec.layers[0].part("mixer_norm")["gain"] == 0.7 and spec.final_norm.get("gain") is None
 
 
+def test_a_layer_may_run_a_later_layers_tensors():
+    c = config()
+    c["layers"][0]["weights_of"] = 3
+    del c["layers"][3]["weights_of"]
+    cfg, spec = resolve(c)
+    assert [layer.prefix for layer in spec.layers] == ["l1", "l2", "l3"]
+    assert [e.layer for e in spec.order] == [2, 0, 1, 2, 1]
+    assert "l3.mix.q" in expected_tensors_of_spec(spec) and "l0.mix.q" not in expected_tensors_of_spec(spec)
+
+
 def test_optional_pieces():
     c = config()
     del c["layers"][1]["mixer"]["rot"]["scaling"]

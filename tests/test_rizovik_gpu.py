@@ -654,6 +654,27 @@ def test_mixed_heads_over_values_too_wide_for_one_pass(tmp_path, dtype):
         check_against_plain(got, refs, dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_proportions(tmp_path, dtype):
+    """Blocks of six under pages of sixteen, more kept positions than the window holds, eight query heads a KV head,
+    heads 40 and 72 wide, five taps, three of seven experts, an odd vocabulary, and a layer that runs the tensors of a
+    LATER layer."""
+    from mini_hisparse_b200 import write_random_model
+
+    att = pooled(8, 1, 40, 72, 11, 6, rot=40, base=200.0, scale=0.2)
+    ff = moe(7, 3, 40)
+    cfg = model(257, 120, [layer("attention", att, ff, weights_of=2), layer("attention_2", kept(8, 1, 24, 40, 6, 9, rot=8), moe(2, 2, 24)),
+                           layer("attention", att, ff), layer("delta", delta(6, 2, 40, 24, 5), moe(5, 2, 32))], mult=0.3)
+    write_random_model(cfg, 17, tmp_path, dtype=torch.bfloat16, matrix_std=0.15)
+    cfg, w = P.load_folder(tmp_path)
+    assert "l2.mix.q" in w and "l0.mix.q" not in w
+    reqs = requests_for(cfg, [90, 37, 5], seed=33)
+    refs = {rid: P.forward(cfg, w, toks).float() for rid, toks in reqs.items()}
+    for steps in (S.whole(reqs), S.mixed(reqs, seed=2, tail=15)):
+        got, stats, pages = run_steps(tmp_path, dtype, steps)
+        check_against_plain(got, refs, dtype)
+
+
 def test_the_plain_model_is_sensitive_to_what_the_tests_are_for(models):
     """A window one key off, a block size or a kept count one off, unscaled frequencies, heads that are not mixed, a
     multiplier, a filter's tap, a layer that runs its own tensors instead of another's: each moves the plain model's
